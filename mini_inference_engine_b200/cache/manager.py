@@ -29,9 +29,11 @@ RELEASED = 0   # block-table entry of a page the window has passed: the scratch 
 
 @dataclass(frozen=True)
 class GroupSpec:
-    """A group of layers with the same need: ``window`` None keeps all positions."""
+    """A group of layers with the same need: ``window`` and ``chunk`` None keeps all positions, ``window`` the last
+    that many, ``chunk`` those of the newest token's own block of that many positions (counted from position 0)."""
     name: str
     window: int | None = None
+    chunk: int | None = None
 
 
 @dataclass
@@ -62,13 +64,16 @@ class CacheManager:
         self.block_size = block_size
         counts = num_pages if isinstance(num_pages, (list, tuple)) else [num_pages] * len(groups)
         self.pools = [PagePool(n) for n in counts]
-        self._windowed = any(g.window is not None for g in self.groups)
+        self._windowed = any(g.window is not None or g.chunk is not None for g in self.groups)
         # slot 0 is the scratch slot of padding rows, like page 0
         self.state_pool = PagePool(num_state_slots + 1) if num_state_slots > 0 else None
 
     # ------------------------------------------------------------------ sizes
     def _first_needed_page(self, g: int, num_computed: int) -> int:
-        w = self.groups[g].window
+        w, c = self.groups[g].window, self.groups[g].chunk
+        if c is not None:
+            # the next query is at position num_computed and reads the keys of its own block of c positions
+            return (num_computed // c * c) // self.block_size
         if w is None:
             return 0
         # the next query is at position num_computed and reads keys > num_computed - w

@@ -26,20 +26,32 @@ class CacheLayout:
     groups: list = field(default_factory=list)
     kv: dict = field(default_factory=dict)
     state: dict = field(default_factory=dict)
+    composite: dict = field(default_factory=dict)      # cache id -> number of entries, for mixers made of several
 
     @classmethod
     def from_needs(cls, needs: dict) -> "CacheLayout":
         """``needs[cache id]`` is what the mixer that uses it declared (None, KVNeed or StateNeed)."""
         lay = cls()
-        windows = sorted({n.window for n in needs.values() if isinstance(n, KVNeed)},
-                         key=lambda w: (w is not None, w or 0))
-        index = {}
-        for w in windows:
-            index[w] = len(lay.groups)
-            lay.groups.append(GroupSpec("full" if w is None else f"window{w}", w))
+        # a mixer made of several declares a tuple of needs: entry i of cache id c is stored under (c, i)
+        flat = {}
         for layer, n in needs.items():
+            if isinstance(n, (tuple, list)):
+                lay.composite[layer] = len(n)
+                for i, m in enumerate(n):
+                    flat[(layer, i)] = m
+            else:
+                flat[layer] = n
+        kinds = sorted({(n.window, n.chunk) for n in flat.values() if isinstance(n, KVNeed)},
+                       key=lambda wc: (wc[0] is not None, wc[0] or 0, wc[1] is not None, wc[1] or 0))
+        index = {}
+        for w, c in kinds:
+            if w is not None and c is not None:
+                raise ValueError("a layer keeps a window or a block of positions, not both")
+            index[(w, c)] = len(lay.groups)
+            lay.groups.append(GroupSpec("full" if w is None and c is None else (f"window{w}" if c is None else f"chunk{c}"), w, c))
+        for layer, n in flat.items():
             if isinstance(n, KVNeed):
-                lay.kv[layer] = (index[n.window], n)
+                lay.kv[layer] = (index[(n.window, n.chunk)], n)
             elif isinstance(n, StateNeed):
                 lay.state[layer] = n
             elif n is not None:
@@ -78,6 +90,9 @@ class CacheStorage:
 
     def layer_cache(self, owner: int, writes: bool = True) -> LayerCache:
         lc = LayerCache(writes=writes, page_size=self.page_size)
+        if owner in self.layout.composite:
+            lc.parts = [self.layer_cache((owner, i), writes) for i in range(self.layout.composite[owner])]
+            return lc
         if owner in self.kv:
             lc.group = self.layout.kv[owner][0]
             lc.k, lc.v = self.kv[owner][0], self.kv[owner][1]

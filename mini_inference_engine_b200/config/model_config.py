@@ -37,6 +37,7 @@ class LayerSpec:
     ``layer.mixer`` is ``layer.parts["mixer"]``."""
     block: str
     parts: dict
+    params: dict = field(default_factory=dict)     # constructor parameters of the block itself (constants of the arrangement)
 
     def __getattr__(self, role):
         parts = object.__getattribute__(self, "parts")
@@ -47,7 +48,7 @@ class LayerSpec:
 
     def with_part(self, role: str, spec: PartSpec) -> "LayerSpec":
         """A copy of this layer with one part exchanged (or added)."""
-        return LayerSpec(self.block, {**self.parts, role: spec})
+        return LayerSpec(self.block, {**self.parts, role: spec}, dict(self.params))
 
 
 @dataclass(frozen=True)
@@ -74,6 +75,8 @@ class ModelSpec:
     eos_token_id: int
     # checkpoint tensors that the model does not read and that are no error when present (fnmatch patterns)
     ignore: tuple = ()
+    # tensors whose name in the checkpoint is not prefix + local name: {name the parts expect: name in the checkpoint}
+    aliases: dict = field(default_factory=dict)
 
 
 _REQUIRED = ("vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers",

@@ -4,6 +4,7 @@ turns config.json into a ``ModelSpec`` that the generic model builds from regist
 The reference has no registry (inference_engine/engine.py:44 builds Llama for anything)."""
 from __future__ import annotations
 
+from .getizen_config import GetizenConfig
 from .model_config import ConfigError, LlamaConfig, read_config_json
 
 _ARCHITECTURES: dict[str, type] = {}
@@ -30,12 +31,15 @@ def load_config(path_or_dict):
     architecture it names."""
     c = path_or_dict if isinstance(path_or_dict, dict) else read_config_json(path_or_dict)
     arch = c.get("architectures")
+    if isinstance(c.get("architecture"), str) and not arch:       # some designs name themselves with a plain string
+        arch = [c["architecture"]]
     if not arch or not isinstance(arch, list):
-        raise ConfigError("config.json lacks 'architectures' (a list with the architecture's name)")
+        raise ConfigError("config.json lacks 'architectures' (a list with the architecture's name) or 'architecture' (the name)")
     return config_class_for(str(arch[0])).from_dict(c)
 
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
+register_architecture("Getizen", GetizenConfig)
 
 
 def preset_names() -> list[str]:

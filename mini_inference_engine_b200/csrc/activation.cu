@@ -83,3 +83,69 @@ extern "C" int mie_swiglu(const void* gu, void* out, int act_tag, int num_tokens
         return launch_kernel(swiglu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out, total, inter, interleaved);
     return MIE_ERR_BAD_ARG;
 }
+
+// A gated feed-forward activation with clamps, on a fused projection [gate | up] (gate first, `inter` columns each):
+//   g = min(gate, limit), u = clamp(up, -limit, limit);  out = g * sigmoid(slope * g) * (u + shift)
+// computed in float32 and rounded once.  limit <= 0 means no clamp.
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int inter, float limit,
+                                   float slope, float shift) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / inter;
+        const int i = (int)(idx - t * inter);
+        float g = to_f32<T>(gu[t * 2 * inter + i]);
+        float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+        if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        out[idx] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
+    }
+}
+
+extern "C" int mie_glu_clamped(const void* gu, void* out, int act_tag, int num_tokens, int inter, float limit, float slope,
+                               float shift, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (inter <= 0) return MIE_ERR_BAD_ARG;
+    const int64_t total = (int64_t)num_tokens * inter;
+    const int threads = 256;
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    if (act_tag == MIE_F32)
+        return launch_kernel(glu_clamped_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inter, limit, slope, shift);
+    else if (act_tag == MIE_BF16)
+        return launch_kernel(glu_clamped_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out, total, inter, limit, slope, shift);
+    return MIE_ERR_BAD_ARG;
+}
+
+// An output gate on attention heads: out[t, h * Dv + c] = attn[t, h, c] * sigmoid(g[t, h * Dv + c]) for c < Dv, where
+// attn rows hold H heads of DP >= Dv entries (the padded tail is dropped) and g is a part of a fused projection
+// with row stride `g_stride`.
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ attn, const T* __restrict__ g, int64_t g_stride, T* __restrict__ out,
+                                    int64_t total, int H, int Dv, int DP) {
+    pdl_enter();
+    const int n = H * Dv;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / n;
+        const int i = (int)(idx - t * n);
+        const int h = i / Dv, c = i - h * Dv;
+        const float z = to_f32<T>(g[t * g_stride + i]);
+        out[idx] = from_f32<T>(to_f32<T>(attn[(t * H + h) * DP + c]) / (1.0f + expf(-z)));
+    }
+}
+
+extern "C" int mie_sigmoid_gate(const void* attn, const void* g, long long g_stride, void* out, int act_tag, int num_tokens,
+                                int H, int Dv, int DP, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (H <= 0 || Dv <= 0 || DP < Dv) return MIE_ERR_BAD_ARG;
+    const int64_t total = (int64_t)num_tokens * H * Dv;
+    const int threads = 256;
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    if (act_tag == MIE_F32)
+        return launch_kernel(sigmoid_gate_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)attn, (const float*)g, (int64_t)g_stride, (float*)out, total, H, Dv, DP);
+    else if (act_tag == MIE_BF16)
+        return launch_kernel(sigmoid_gate_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)attn, (const bf16*)g, (int64_t)g_stride, (bf16*)out, total, H, Dv, DP);
+    return MIE_ERR_BAD_ARG;
+}

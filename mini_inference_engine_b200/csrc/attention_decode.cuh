@@ -106,8 +106,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     const int quad = lane >> 2, tq = lane & 3;
 
     // this block's part of the context: the range [lo, ctx) cut into `splits` parts of whole tiles
-    const int lo = p.window > 0 ? (max(0, ctx - p.window) & ~(DEC_TILE - 1)) : 0;
-    const int first_key = p.window > 0 ? max(0, ctx - p.window) : 0;
+    const int first_key = mask_first_key(ctx - 1, p.window);      // sliding window, or the start of the query's block of positions
+    const int lo = first_key & ~(DEC_TILE - 1);
     const int tiles_total = (ctx - lo + DEC_TILE - 1) / DEC_TILE;
     // The grid is laid out for the longest context the launch may meet; a row is cut into as many parts as
     // its own length pays for (scratch merge only: the blocks of a cluster all take part in its barriers).

@@ -67,7 +67,7 @@ prefill_attention_kernel(const PrefillParams p) {
     const int pos0 = ctx - q_len + q0;                              // position of the tile's first query
     const int nq = min(PRE_BM, q_len - q0);                         // queries in this tile
     const int k_hi = pos0 + nq;                                     // one past the last key any query reads
-    const int k_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int k_lo = mask_first_key(pos0, p.window);
     const int kbeg = k_lo & ~(PRE_BN - 1);
     const int ntiles = (k_hi - kbeg + PRE_BN - 1) / PRE_BN;
 
@@ -148,7 +148,7 @@ prefill_attention_kernel(const PrefillParams p) {
             }
             // only tiles that touch the diagonal, the window's edge or the range's start need masking
             const bool need_mask = key0 + PRE_BN - 1 > pos0 + wq || key0 < k_lo ||
-                                   (p.window > 0 && key0 <= pos0 + wq + 15 - p.window);
+                                   (p.window != 0 && key0 < mask_first_key(pos0 + wq + 15, p.window));
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int n = 0; n < PRE_BN / 8; ++n)
@@ -158,7 +158,7 @@ prefill_attention_kernel(const PrefillParams p) {
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int qp = qpos[i >> 1];
-                        const bool ok = key <= qp && (p.window <= 0 || key > qp - p.window);
+                        const bool ok = key <= qp && key >= mask_first_key(qp, p.window);
                         v = ok ? v : -INFINITY;
                     }
                     s[n][i] = v;

@@ -194,7 +194,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
             g.pos0 = ctx - q_len + g.q0;                         // position of the tile's first query
             g.nq = min(FA_BM, q_len - g.q0);
             g.k_hi = g.pos0 + g.nq;                              // one past the last key any query here reads
-            g.k_lo = p.window > 0 ? max(0, g.pos0 - p.window + 1) : 0;
+            g.k_lo = mask_first_key(g.pos0, p.window);
             g.kbeg = g.k_lo & ~(FA_BN - 1);
             g.ntiles = u < nsub ? (g.k_hi - g.kbeg + FA_BN - 1) / FA_BN : 0;
         }
@@ -348,7 +348,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     tc_fence_after();
                     const int key0 = kbeg + t * FA_BN;
                     // masks are needed only where the tile touches the diagonal, the window's edge or the range's start
-                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
+                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window != 0 && key0 < mask_first_key(pos0 + FA_BM - 1, p.window));
                     // The row of S comes out of TMEM in four chunks of 32 columns; the load of the next chunk is
                     // in flight while the current one is worked on.
                     auto for_each_chunk = [&](auto&& body) {
@@ -366,7 +366,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         tmem_ld_wait(cb);
                         body(3, cb);
                     };
-                    auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
+                    auto masked = [&](int key) { return !(key <= qpos && key >= mask_first_key(qpos, p.window)); };
                     // Reference point of the exponent.  Reading S once per tile is what matters here (TMEM
                     // loads are the slowest part of the step), so the running max is not recomputed up front:
                     // P is formed against the running max as it stands, the row's true max is found on the
@@ -605,7 +605,7 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             g.pos0 = ctx - q_len + g.q0;
             g.nq = min(FA_BM, q_len - g.q0);
             g.k_hi = g.pos0 + g.nq;
-            g.k_lo = p.window > 0 ? max(0, g.pos0 - p.window + 1) : 0;
+            g.k_lo = mask_first_key(g.pos0, p.window);
         }
         // one grid of key tiles for both query tiles, from the first key the first tile reads
         const int kbeg = sb[0].k_lo & ~(FA_BN - 1);
@@ -747,7 +747,7 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tc_fence_after();
                     if (q == 2 && lane == 0) { PP_STAMP(u, j, 0); }
                     const int key0 = kbeg + j * FA_BN;
-                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window > 0 && key0 <= pos0 + FA_BM - 1 - p.window);
+                    const bool need_mask = key0 + FA_BN - 1 > pos0 || key0 < k_lo || (p.window != 0 && key0 < mask_first_key(pos0 + FA_BM - 1, p.window));
                     // The whole row of S moves into registers at once and S is given back (s_free): the MMA thread
                     // issues this group's scores of the next key tile while the exponentials below run out of
                     // registers.  A row that has to be redone against a new maximum is redone from registers too.
@@ -761,7 +761,7 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&s_free[u]);
                     if (q == 2 && lane == 0) { PP_STAMP(u, j, 1); }
-                    auto masked = [&](int key) { return !(key <= qpos && (p.window <= 0 || key > qpos - p.window)); };
+                    auto masked = [&](int key) { return !(key <= qpos && key >= mask_first_key(qpos, p.window)); };
                     if (need_mask) {                               // masked entries become -inf once, here
 #pragma unroll
                         for (int i = 0; i < 128; ++i) if (masked(key0 + i)) sv[i] = __float_as_uint(-INFINITY);

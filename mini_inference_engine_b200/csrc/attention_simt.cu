@@ -4,7 +4,7 @@
 //
 // A batch row is a request: q_len new tokens whose keys and values were already written to the
 // cache, ctx_len = tokens in the cache including them.  Query i of the row sits at position
-// p = ctx_len - q_len + i and reads keys j <= p (and j > p - window when window > 0) through the
+// p = ctx_len - q_len + i and reads keys j <= p (from mask_first_key(p, window) on: a sliding window or its own block of positions) through the
 // row's block table.  Query head h reads kv head h / (H / H_kv).  Scores, softmax and the
 // accumulator are float32; online softmax over tiles of 32 keys.
 //
@@ -97,7 +97,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
 
     const int q_last = min(q0 + QT, q_len) - 1;
     const int k_hi = ctx_len - q_len + q_last + 1;                       // one past the last key any query here reads
-    const int k_lo = window > 0 ? max(0, ctx_len - q_len + q0 - window + 1) : 0;
+    const int k_lo = mask_first_key(ctx_len - q_len + q0, window);
 
     float m = -INFINITY, l = 0.f;
     float acc[ATT_MAX_D / 32];
@@ -129,7 +129,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
         __syncthreads();
         if (active) {
             const int key = k0 + lane;
-            const bool valid = key <= pos_q && (window <= 0 || key > pos_q - window);
+            const bool valid = key <= pos_q && key >= mask_first_key(pos_q, window);
             float s = 0.f;
             const float4* kr = reinterpret_cast<const float4*>(k_s + lane * DP);
             const float4* qr = reinterpret_cast<const float4*>(q_s + warp * D);

@@ -16,6 +16,16 @@
 
 typedef __nv_bfloat16 bf16;
 
+// Which keys a query may read besides "not later than itself", as one integer `window`:
+//   0   every earlier key;   w > 0   the last w positions (a sliding window);
+//   w < 0   the keys of the query's own block of -w positions, blocks counted from position 0 (chunked attention).
+// Returns the first key position that a query at `pos` reads; it never decreases with `pos`.
+__host__ __device__ __forceinline__ int mask_first_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

@@ -57,13 +57,19 @@ def rotates_in_decode(dtype, head_dim: int, ctx) -> bool:
             and decode_only(ctx))
 
 
-def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window, rope=None):
+def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window, rope=None, q_stride=None):
     """``rope`` = (cos, sin): ``qkv`` is unrotated and the cache rows of the new tokens are unwritten; only
-    where ``rotates_in_decode`` holds."""
-    q_stride = (num_heads + 2 * num_kv_heads) * head_dim
+    where ``rotates_in_decode`` holds.  ``window``: None or 0 all earlier keys, w > 0 the last w positions, w < 0 the
+    keys of the query's own block of -w positions.  ``q_stride``: elements between the token rows of ``qkv`` (by
+    default rows of a fused q|k|v projection)."""
+    if q_stride is None:
+        q_stride = (num_heads + 2 * num_kv_heads) * head_dim
     args = (qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start, ctx.row_q_len,
             ctx.row_ctx_len)
     fast = _backend == "auto" and qkv.dtype == torch.bfloat16 and head_dim <= 128
+    window = int(window or 0)
+    # the keys a single new token can reach, for the decode kernel's plan: a window or a block of positions bounds them
+    reach = ctx.max_ctx_len if window == 0 else min(ctx.max_ctx_len, abs(window) + 64)
     if rope is not None:
         if not rotates_in_decode(qkv.dtype, head_dim, ctx):
             raise ValueError("rotation inside attention serves steps of decoding rows only (bfloat16, head sizes "
@@ -83,7 +89,7 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         has_decode, min_q_len = False, 1
     if has_decode:
         ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
-                             max_ctx=ctx.max_ctx_len)
+                             max_ctx=reach)
     if has_prefill:
         # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
         tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"

@@ -77,7 +77,8 @@ _RANGE_CODES = {1: "token id outside the vocabulary (or the fed-back tokens)", 2
                 "(or more positions than the block table covers)", 3: "cache slot outside the cache",
                 4: "block-table entry outside the page pool", 5: "row index outside the batch"}
 _RANGE_KERNELS = {1: "embedding", 2: "rope_cache", 3: "norm", 4: "attention_simt", 5: "attention_decode",
-                  6: "attention_prefill", 7: "attention_prefill_tc", 8: "gemm_tcgen05 (q|k|v with rotation)"}
+                  6: "attention_prefill", 7: "attention_prefill_tc", 8: "gemm_tcgen05 (q|k|v with rotation)",
+                  9: "norm_group", 10: "qk_norm_rope"}
 _range_report: torch.Tensor | None = None
 _range_told: set = set()
 
@@ -538,6 +539,200 @@ def sample(logits: torch.Tensor, temperature, request, position, seed: int, out:
     _check(lib.mie_sample(_ptr(logits), _ptr(temperature), _ptr(request), _ptr(position),
                           ctypes.c_uint64(seed & ((1 << 64) - 1)), _ptr(out), rows, vocab, host_ptr,
                           _ptr(host_turn) if host_out is not None else ctypes.c_void_p(0), stride, _stream()), "sample")
+    return out
+
+
+# --------------------------------------------------------------------------- post-norm stream, grouped statistics
+
+def _tagged(t):
+    return (_ptr(t), tag(t)) if t is not None else (ctypes.c_void_p(0), 0)
+
+
+def stream_norm(res: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out: torch.Tensor | None = None, *,
+                alpha: float = 1.0, deltas=(), inner_weights=(), coef: float = 1.0, rows: torch.Tensor | None = None):
+    """res <- gnorm(alpha * res + coef * sum_k b_k) * weight in place (float32), where b_k is ``deltas[k]`` or, with
+    ``inner_weights[k]``, that delta RMS-normed over its whole row and multiplied by the weight; gnorm divides each
+    of ``groups`` equal consecutive parts of a row by its own root mean square.  ``out`` (optional) receives the
+    result in its own type.  With ``rows`` output row b comes from stream row rows[b] and ``res`` is not written."""
+    n = res.shape[-1]
+    _need(res.dtype == torch.float32 and res.is_contiguous(), "the residual stream must be contiguous float32")
+    _need(weight.numel() == n and weight.is_contiguous(), f"norm weight must have {n} entries")
+    _need(groups >= 1 and n % groups == 0, f"{groups} groups do not divide a row of {n}")
+    _need(len(deltas) <= 2, "at most two branches are added")
+    deltas = list(deltas) + [None] * (2 - len(deltas))
+    inner = list(inner_weights) + [None] * (2 - len(inner_weights))
+    d_tags = {tag(d) for d in deltas if d is not None}
+    i_tags = {tag(w) for w in inner if w is not None}
+    _need(len(d_tags) <= 1 and len(i_tags) <= 1, "branches (and their weights) must share a type")
+    for d in deltas:
+        if d is not None:
+            _need(d.shape == res.shape and d.is_contiguous(), "a branch must match the stream's shape")
+    for w in inner:
+        if w is not None:
+            _need(w.numel() == n and w.is_contiguous(), f"a branch's norm weight must have {n} entries")
+    num_rows = res.shape[0]
+    if rows is not None:
+        _i32(rows, "rows")
+        num_rows = rows.numel()
+        _need(out is not None, "gathered rows need an output")
+    if out is not None:
+        _need(out.is_contiguous() and out.shape == (num_rows, n), "norm output must be contiguous [rows, n]")
+    lib = load("norm_group")
+    _check(lib.mie_stream_norm(_ptr(res), ctypes.c_float(alpha), _ptr(deltas[0]), _ptr(inner[0]), _ptr(deltas[1]), _ptr(inner[1]),
+                               d_tags.pop() if d_tags else 0, i_tags.pop() if i_tags else 0, ctypes.c_float(coef),
+                               _ptr(weight), tag(weight), int(groups), ctypes.c_float(eps), _ptr(out),
+                               tag(out) if out is not None else 0, _ptr(rows), num_rows, n, res.shape[0], _stream()),
+           "stream_norm")
+    return out
+
+
+# --------------------------------------------------------------------------- q/k norm, rotation, padded cache write
+
+def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out: torch.Tensor, k_cache, v_cache, *,
+                 num_heads: int, num_kv_heads: int, dim: int, vdim: int, rot: int, page_size: int, eps: float = 0.0,
+                 q_weight=None, k_weight=None, temp=None, q_scale: float = 1.0, k_scale: float = 1.0,
+                 write_cache: bool = True) -> torch.Tensor:
+    """From the fused projection rows [q: H x dim | k: G x dim | v: G x vdim | ...]: q and k optionally RMS-normed over
+    their whole projection, rotated by position x ``freq`` over their first ``rot`` dims, q scaled per head, q written to
+    ``q_out`` [T, H, DP] and k, v to their cache slots (pages [page, G, page_size, DP], tails zero)."""
+    T = qkv.shape[0]
+    DP = q_out.shape[-1]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= (num_heads + num_kv_heads) * dim + num_kv_heads * vdim,
+          "qkv rows must hold q, k and v")
+    _need(q_out.is_contiguous() and q_out.shape == (T, num_heads, DP) and q_out.dtype == qkv.dtype, "q_out must be [T, H, DP]")
+    _need(k_cache.dtype == qkv.dtype == v_cache.dtype and k_cache.shape[-1] == DP and k_cache.is_contiguous(), "cache type and width")
+    _need(freq.dtype == torch.float32 and freq.numel() * 2 == rot and freq.is_contiguous(), "one float32 frequency per rotated pair")
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    ws = [w for w in (q_weight, k_weight, temp) if w is not None]
+    _need(len({w.dtype for w in ws}) <= 1 and all(w.is_contiguous() for w in ws), "norm weights and temperatures must share a type")
+    if q_weight is not None:
+        _need(q_weight.numel() == num_heads * dim, "q norm weight size")
+    if k_weight is not None:
+        _need(k_weight.numel() == num_kv_heads * dim, "k norm weight size")
+    if temp is not None:
+        _need(temp.numel() == num_heads, "one temperature per head")
+    lib = load("qk_norm_rope")
+    _check(lib.mie_qk_norm_rope(_ptr(qkv), tag(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(positions), _ptr(slots), _ptr(freq),
+                                _ptr(q_weight), _ptr(k_weight), _ptr(temp), tag(ws[0]) if ws else 0, ctypes.c_float(eps),
+                                ctypes.c_float(q_scale), ctypes.c_float(k_scale), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), T,
+                                num_heads, num_kv_heads, dim, vdim, DP, rot, page_size, ctypes.c_longlong(k_cache.shape[0]),
+                                int(write_cache), _stream()), "qk_norm_rope")
+    return q_out
+
+
+# --------------------------------------------------------------------------- retention
+
+def retention_scan(qkv: torch.Tensor, row_q_start, row_q_len, row_ctx_len, state_slots, decay, freq, state, out, *,
+                   num_heads: int, dim: int, vdim: int, rot: int, k_scale: float) -> torch.Tensor:
+    """S <- decay_h S + k v^T, o = S^T q for every new token of every row, from and to ``state`` [slots, H, vdim, dim]
+    float32; q and k are rotated inside.  ``qkv`` rows hold [q: H x dim | k: H x dim | v: H x vdim | ...];
+    ``out`` [T, H * vdim] float32."""
+    T = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= num_heads * (2 * dim + vdim), "qkv rows must hold q, k and v")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (num_heads, vdim, dim),
+          "state must be float32 [slots, H, vdim, dim]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, num_heads * vdim), "out must be float32 [T, H * vdim]")
+    _need(decay.dtype == torch.float32 and decay.numel() == num_heads, "one float32 decay per head")
+    _need(freq.dtype == torch.float32 and freq.numel() * 2 == rot, "one float32 frequency per rotated pair")
+    for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (row_ctx_len, "row_ctx_len"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("retention")
+    _check(lib.mie_retention_scan(_ptr(qkv), tag(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(row_q_start), _ptr(row_q_len),
+                                  _ptr(row_ctx_len), _ptr(state_slots), _ptr(decay), _ptr(freq), ctypes.c_float(k_scale),
+                                  _ptr(state), _ptr(out), row_q_len.numel(), num_heads, dim, vdim, rot, _stream()), "retention_scan")
+    return out
+
+
+def head_rms_gate(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, vdim: int, eps: float) -> torch.Tensor:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * silu(gate[t, h]) per head of ``vdim`` entries; ``gate`` may be a column
+    slice of a wider tensor."""
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, num_heads * vdim), "o must be float32 [T, H * vdim]")
+    _need(gate.stride(1) == 1 and gate.shape == o.shape and gate.dtype == out.dtype, "gate must match o's shape and the output's type")
+    _need(out.is_contiguous() and out.shape == o.shape, "out must be contiguous [T, H * vdim]")
+    lib = load("retention")
+    _check(lib.mie_head_rms_gate(_ptr(o), _ptr(gate), tag(gate), ctypes.c_longlong(gate.stride(0)), _ptr(out), T, num_heads, vdim,
+                                 ctypes.c_float(eps), _stream()), "head_rms_gate")
+    return out
+
+
+# --------------------------------------------------------------------------- gated linear recurrence
+
+def causal_conv(x: torch.Tensor, ctx_token_row, row_q_start, state_slots, taps, bias, state, u) -> torch.Tensor:
+    """u[t] = bias + sum_j taps[:, j] x[t - (K-1) + j] per channel; inputs older than a row's portion come from rows
+    1.. of ``state`` [slots, K, C] float32.  ``x`` may be a column slice; ``u`` float32 [T, C]."""
+    T, C = x.shape
+    K = taps.shape[1]
+    _need(x.stride(1) == 1 and taps.shape == (C, K) and taps.is_contiguous(), "conv taps must be [channels, taps]")
+    _need(bias is None or (bias.dtype == taps.dtype and bias.numel() == C), "conv bias must match the taps")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (K, C), "state must be float32 [slots, K, C]")
+    _need(u.dtype == torch.float32 and u.is_contiguous() and u.shape == (T, C), "u must be float32 [T, C]")
+    for t, n in ((ctx_token_row, "token_row"), (row_q_start, "row_q_start"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("linear_recurrence")
+    _check(lib.mie_causal_conv(_ptr(x), tag(x), ctypes.c_longlong(x.stride(0)), _ptr(ctx_token_row), _ptr(row_q_start),
+                               _ptr(state_slots), _ptr(taps), _ptr(bias), tag(taps), _ptr(state), _ptr(u), T, C, K, _stream()),
+           "causal_conv")
+    return u
+
+
+def recurrence_gates(u, w_a, b_a, w_i, b_i, lam, c_exp: float, a_out, b_out) -> None:
+    """Block-diagonal gates and the recurrence's coefficients: a = exp(-c_exp * sigmoid(Wa u + ba) * softplus(lam)),
+    b = sqrt(1 - a^2) * sigmoid(Wi u + bi) * u, float32."""
+    T, C = u.shape
+    B, bw = w_a.shape[0], w_a.shape[1]
+    _need(w_a.shape == (B, bw, bw) == w_i.shape and B * bw == C, "gate matrices must be [blocks, C / blocks, C / blocks]")
+    ws = (w_a, b_a, w_i, b_i, lam)
+    _need(len({w.dtype for w in ws}) == 1 and all(w.is_contiguous() for w in ws), "gate weights must share a type")
+    _need(b_a.numel() == C == b_i.numel() == lam.numel(), "gate biases and lam have one entry per channel")
+    for t in (u, a_out, b_out):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, C), "u, a and b must be float32 [T, C]")
+    lib = load("linear_recurrence")
+    _check(lib.mie_recurrence_gates(_ptr(u), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(lam), tag(w_a), ctypes.c_float(c_exp),
+                                    _ptr(a_out), _ptr(b_out), T, C, B, _stream()), "recurrence_gates")
+
+
+def recurrence_scan(a, b, y, x, row_q_start, row_q_len, state_slots, state, out, segments: int = 1) -> torch.Tensor:
+    """s <- a s + b along every row's tokens from ``state`` [slots, K, C] (row 0), out = s * gelu_tanh(y); the last K-1
+    inputs ``x`` of the convolution are moved into rows 1.. of the state.  ``x`` and ``y`` may be column slices."""
+    T, C = a.shape
+    K = state.shape[1]
+    _need(x.stride(1) == 1 and y.stride(1) == 1 and x.shape == (T, C) == y.shape and x.dtype == y.dtype == out.dtype, "x, y must be [T, C]")
+    _need(out.is_contiguous() and out.shape == (T, C), "out must be contiguous [T, C]")
+    for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("linear_recurrence")
+    _check(lib.mie_recurrence_scan(_ptr(a), _ptr(b), _ptr(y), tag(y), ctypes.c_longlong(y.stride(0)), _ptr(x),
+                                   ctypes.c_longlong(x.stride(0)), _ptr(row_q_start), _ptr(row_q_len), _ptr(state_slots),
+                                   _ptr(state), _ptr(out), row_q_len.numel(), C, K, int(segments), _stream()), "recurrence_scan")
+    return out
+
+
+# --------------------------------------------------------------------------- gated activations
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float) -> torch.Tensor:
+    """out = g * sigmoid(slope * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit) from the
+    fused projection [gate | up]; ``limit`` <= 0 leaves both unclamped."""
+    T, two_i = gate_up.shape
+    _need(two_i % 2 == 0 and out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype
+          and out.is_contiguous() and gate_up.is_contiguous(), "glu shapes/types do not match")
+    lib = build.load("activation")
+    _check(lib.mie_glu_clamped(_ptr(gate_up), _ptr(out), tag(out), T, two_i // 2, ctypes.c_float(limit), ctypes.c_float(slope),
+                               ctypes.c_float(shift), _stream()), "glu_clamped")
+    return out
+
+
+def sigmoid_gate(attn: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, vdim: int) -> torch.Tensor:
+    """out[t, h * vdim + c] = attn[t, h, c] * sigmoid(gate[t, h * vdim + c]); ``attn`` [T, H, DP >= vdim], ``gate`` may be a
+    column slice of a wider tensor."""
+    T, DP = attn.shape[0], attn.shape[-1]
+    _need(attn.is_contiguous() and attn.shape == (T, num_heads, DP) and DP >= vdim, "attn must be [T, H, DP]")
+    _need(gate.stride(1) == 1 and gate.shape == (T, num_heads * vdim) and gate.dtype == attn.dtype == out.dtype, "gate must be [T, H * vdim]")
+    _need(out.is_contiguous() and out.shape == (T, num_heads * vdim), "out must be contiguous [T, H * vdim]")
+    lib = build.load("activation")
+    _check(lib.mie_sigmoid_gate(_ptr(attn), _ptr(gate), ctypes.c_longlong(gate.stride(0)), _ptr(out), tag(out), T, num_heads, vdim, DP,
+                                _stream()), "sigmoid_gate")
     return out
 
 

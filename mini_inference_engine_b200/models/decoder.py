@@ -28,7 +28,7 @@ def _layer_parts(layer_spec):
         raise ValueError(f"block {layer_spec.block!r} is made of {', '.join(sorted(roles))}; the layer describes "
                          f"{', '.join(sorted(layer_spec.parts))}")
     built = {role: build_part(roles[role], layer_spec.parts[role]) for role in roles}
-    return cls(**built), [(layer_spec.parts[role].prefix, built[role]) for role in roles]
+    return cls(**built, **layer_spec.params), [(layer_spec.parts[role].prefix, built[role]) for role in roles]
 
 
 class _Skeleton:
@@ -73,7 +73,7 @@ class DecoderModel:
         self.spec = spec
         self.rt = rt
         tied = spec.head.prefix == spec.embedding.prefix
-        tensors = check_and_bind(state, sk.expected(), ignore=tuple(spec.ignore), where=where)
+        tensors = check_and_bind(state, sk.expected(), ignore=tuple(spec.ignore), where=where, aliases=spec.aliases)
         for prefix, part in sk.named:
             local = {n: tensors[prefix + n] for n in part.tensor_specs()}
             part.bind(local, rt)
@@ -132,6 +132,8 @@ class DecoderModel:
     def _step(self, ctx: StepContext) -> torch.Tensor:
         res = self.embedding.forward(ctx)
         delta = None
+        if isinstance(res, tuple):                 # an embedding that hands on more than the stream (its value in the activation type)
+            res, delta = res
         last = len(self.run_order) - 1
         for i, (entry, cache) in enumerate(zip(self.run_order, self._caches)):
             block = self.blocks[entry.layer]

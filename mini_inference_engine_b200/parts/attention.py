@@ -90,4 +90,93 @@ class Attention(Mixer):
         return self.rt.linear(out, self.w_o)
 
 
+class GatedAttention(Mixer):
+    """Grouped-query softmax attention with the extras of some newer designs, each a parameter:
+
+    * key/query size ``dim`` and value size ``vdim`` may differ (pages are as wide as the wider, tails zero);
+    * ``qk_norm``: q and k are RMS-normed over their whole projection (all heads at once) with weights 'q.norm', 'k.norm';
+    * rotation over the first ``rot_dims`` dims with frequencies that may be rescaled by wavelength (``rot_scaling``);
+    * ``head_temp``: the score of head h is multiplied by 'temp'[h] (folded into the query);
+    * ``chunk``: a query sees keys of its own block of that many positions only; ``window``: a sliding window;
+    * ``gate``: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection.
+
+    q, k, v and the gate are one product; norm, rotation, temperature and the cache write one kernel; attention
+    itself is the framework's paged kernels (decode and portions); the gate one more."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
+                 rot_dims: int, rot_base: float, eps: float, rot_scaling: dict | None = None, qk_norm: bool = True,
+                 head_temp: bool = True, gate: bool = True, chunk: int | None = None, window: int | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError(f"rot_dims {rot_dims} must be even and at most dim {dim}")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim = hidden_size, num_heads, num_kv_heads, dim, vdim
+        self.padded = -(-max(dim, vdim) // 16) * 16          # the attention kernels take head sizes in steps of 16
+        if self.padded > 256:
+            raise ValueError(f"heads of {max(dim, vdim)}: the attention kernels take up to 256")
+        self.scale, self.eps = float(scale), eps
+        self.rot_dims, self.rot_base, self.rot_scaling = rot_dims, rot_base, rot_scaling
+        self.qk_norm, self.head_temp, self.gate, self.chunk, self.window = qk_norm, head_temp, gate, chunk, window
+        self.need = KVNeed(num_kv_heads, self.padded, window, chunk)
+
+    def tensor_specs(self):
+        H, G, D, Dv, h = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.hidden_size
+        specs = {"q": TensorSpec((H * D, h), "fan_in"), "k": TensorSpec((G * D, h), "fan_in"), "v": TensorSpec((G * Dv, h), "fan_in"),
+                 "o": TensorSpec((h, H * Dv), "fan_in")}
+        if self.gate:
+            specs["g"] = TensorSpec((H * Dv, h), "fan_in")
+        if self.qk_norm:
+            specs.update({"q.norm": TensorSpec((H * D,), "normal:1:0.1"), "k.norm": TensorSpec((G * D,), "normal:1:0.1")})
+        if self.head_temp:
+            specs["temp"] = TensorSpec((H,), "uniform:0.5:2")
+        return specs
+
+    def bind(self, tensors, rt):
+        from .rope import rotary_frequencies
+        self.rt = rt
+        parts = [tensors[n] for n in ("q", "k", "v") + (("g",) if self.gate else ())]
+        if len({p.dtype for p in parts}) > 1:
+            parts = [p.float() for p in parts]
+        self.w_in = rt.place(torch.cat(parts, 0))
+        self.w_o = rt.place(tensors["o"])
+        small = lambda n: tensors[n].float().to(rt.device).contiguous()        # read as float32 by the kernel
+        self.q_norm = small("q.norm") if self.qk_norm else None
+        self.k_norm = small("k.norm") if self.qk_norm else None
+        self.temp = small("temp") if self.head_temp else None
+        self.freq = rotary_frequencies(self.rot_dims, self.rot_base, self.rot_scaling).to(rt.device)
+
+    def cache_need(self):
+        return self.need
+
+    def kernel_sources(self):
+        names = self.rt.product_sources(self.w_in, self.w_o) | {"qk_norm_rope", "activation"}
+        if self.rt.dtype == torch.float32 or self.padded > 128:
+            names.add("attention_simt")
+        else:
+            names |= {"attention_decode", "attention_prefill_tc" if self.padded in (64, 128) else "attention_prefill"}
+        return names
+
+    def forward(self, x, ctx, cache):
+        from ..kernels import ops
+        H, G, D, Dv, DP = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.padded
+        T = ctx.num_tokens
+        proj = self.rt.linear(x, self.w_in)
+        q = self.rt.empty(T, H, DP)
+        ops.qk_norm_rope(proj, ctx.positions, ctx.slots[cache.group], self.freq, q, cache.k, cache.v, num_heads=H,
+                         num_kv_heads=G, dim=D, vdim=Dv, rot=self.rot_dims, page_size=cache.page_size, eps=self.eps,
+                         q_weight=self.q_norm, k_weight=self.k_norm, temp=self.temp, write_cache=cache.writes)
+        heads = self.rt.empty(T, H, DP)
+        attn_kernels.attention(q, ctx, cache, heads, H, G, DP, self.scale, self.need.mask(), q_stride=H * DP)
+        if self.gate or DP != Dv:
+            gated = self.rt.empty(T, H * Dv)
+            if self.gate:
+                ops.sigmoid_gate(heads, proj[:, (H + G) * D + G * Dv:], gated, H, Dv)
+            else:
+                gated.view(T, H, Dv).copy_(heads[:, :, :Dv])
+        else:
+            gated = heads.view(T, H * Dv)
+        return self.rt.linear(gated, self.w_o, None, out_dtype=torch.float32)
+
+
 register_part("mixer", "attention", Attention)
+register_part("mixer", "gated_attention", GatedAttention)

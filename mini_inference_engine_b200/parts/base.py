@@ -11,7 +11,8 @@ Interfaces (duck-typed; the base classes below only document them and hold the d
   every part      tensor_specs() -> {local tensor name: TensorSpec}
                   bind(tensors: {local name: device tensor}, rt: Runtime) -> None
   norm            __call__(delta | None, res, out_rows=None) -> x      res += delta; x = norm(res)
-  mixer           cache_need() -> KVNeed | StateNeed | None
+  mixer           cache_need() -> KVNeed | StateNeed | None | a tuple of those (a mixer made of several: it is handed
+                  a LayerCache whose ``parts`` holds one LayerCache per entry)
                   forward(x[T, hidden], ctx: StepContext, cache: LayerCache) -> [T, hidden]
   feed-forward    forward(x[T, hidden], ctx) -> [T, hidden]
   position        rotate_and_store(qkv, ctx, cache, heads, kv_heads)   rotate q (in place) and k, write k, v to the cache
@@ -58,10 +59,18 @@ def build_part(category: str, spec: PartSpec):
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Pages of keys and values: all positions (``window`` None) or the last ``window``."""
+    """Pages of keys and values: all positions (``window`` and ``chunk`` None), the last ``window``, or the
+    positions of the newest token's own block of ``chunk`` positions (blocks counted from position 0)."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
+
+    def mask(self) -> int:
+        """The kernels' one integer for this need: 0 all keys, w > 0 a sliding window, -c a block of c positions."""
+        if self.window and self.chunk:
+            raise ValueError("a layer keeps a window or a block of positions, not both")
+        return int(self.window or 0) or -int(self.chunk or 0)
 
 
 @dataclass(frozen=True)
@@ -81,6 +90,7 @@ class LayerCache:
     page_size: int = 0
     state: torch.Tensor | None = None   # [slots + 1, *shape]; slot 0 is scratch
     writes: bool = True             # False when this run of the layer only reads another layer's cache
+    parts: list = field(default_factory=list)   # a mixer made of several (``cache_need()`` returned a tuple): one LayerCache each
 
 
 # --------------------------------------------------------------------------- what a step gives every part
@@ -116,6 +126,14 @@ class ResidualSink:
     its output to ``res`` itself (in its last product's epilogue) and returns a StreamUpdated."""
     res: torch.Tensor
     norm: object
+
+
+@dataclass
+class StreamValue:
+    """Returned by a block whose stream is complete when it returns (nothing is left to be added by the next
+    norm): ``x`` is the stream's value in the activation type, for the next reader (the stream itself in the
+    32-bit mode).  A norm given one treats it as "nothing to add"."""
+    x: torch.Tensor
 
 
 @dataclass

@@ -5,7 +5,7 @@ is fused into the *next* norm, so a block takes the pending ``delta`` and return
 add+norm, after the last layer into the final norm)."""
 from __future__ import annotations
 
-from .base import Part, ResidualSink, register_part
+from .base import Part, ResidualSink, StreamValue, register_part
 
 
 def _sink_for(producer, consumer, norm, res, num_tokens):
@@ -56,3 +56,49 @@ class PreNormResidual(Block):
 
 
 register_part("block", "prenorm_residual", PreNormResidual)
+
+
+class Branches:
+    """What a mixer may return instead of one tensor: several outputs that the block's norm adds together, each
+    optionally RMS-normed over its row with ``inner_weights[k]`` first, the sum multiplied by ``coef``."""
+
+    def __init__(self, deltas, inner_weights=(), coef: float = 1.0):
+        self.deltas, self.inner_weights, self.coef = tuple(deltas), tuple(inner_weights), coef
+
+
+class PostNormResidual(Block):
+    """Norm after the sum: x <- mixer_norm(alpha x + mixer(x)), then x <- feed_forward_norm(alpha x + ff(x)); both
+    sublayers read the stream itself.  The sum and the norm are one kernel (the norm's ``apply``), which also leaves
+    the stream in the activation type for the next reader.  ``feed_forward`` may be absent (``has_feed_forward``
+    False): the layer is then its mixer half only."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
+    def __init__(self, alpha: float = 1.0, **parts):
+        super().__init__(**parts)
+        self.alpha = float(alpha)
+
+    def _summed(self, norm, res, y):
+        if isinstance(y, Branches):
+            return norm.apply(res, y.deltas, y.inner_weights, alpha=self.alpha, coef=y.coef)
+        return norm.apply(res, (y,), alpha=self.alpha)
+
+    def forward(self, delta, res, ctx, cache):
+        if isinstance(delta, StreamValue):
+            x = delta.x
+        else:
+            if delta is not None:
+                raise ValueError("a post-norm block cannot take a pending sum from the block before it")
+            x = res if self.mixer.rt.dtype == res.dtype else res.to(self.mixer.rt.dtype)
+        x = self._summed(self.mixer_norm, res, self.mixer.forward(x, ctx, cache))
+        if getattr(self, "feed_forward", None) is not None:
+            x = self._summed(self.feed_forward_norm, res, self.feed_forward.forward(x, ctx))
+        return StreamValue(x)
+
+
+class PostNormMixerOnly(PostNormResidual):
+    """The same without a feed-forward half."""
+    roles = {"mixer": "mixer", "mixer_norm": "norm"}
+
+
+register_part("block", "postnorm_residual", PostNormResidual)
+register_part("block", "postnorm_mixer_only", PostNormMixerOnly)

@@ -53,3 +53,33 @@ class LinearHead(Part):
 
 register_part("embedding", "embedding", Embedding)
 register_part("head", "linear_head", LinearHead)
+
+
+class NormedEmbedding(Embedding):
+    """A token embedding followed by a norm of the stream (``norm``: the PartSpec of a norm with an ``apply``; its
+    tensors are 'norm.<its own>').  Hands on the stream and its value in the activation type."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, norm):
+        super().__init__(vocab_size, hidden_size)
+        from .base import build_part
+        self.norm = build_part("norm", norm)
+
+    def tensor_specs(self):
+        specs = {"weight": TensorSpec((self.vocab_size, self.hidden_size), "normal:0:1")}
+        specs.update({"norm." + k: v for k, v in self.norm.tensor_specs().items()})
+        return specs
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.norm.bind({k: tensors["norm." + k] for k in self.norm.tensor_specs()}, rt)
+
+    def kernel_sources(self):
+        return {"embedding"} | self.norm.kernel_sources()
+
+    def forward(self, ctx):
+        from .base import StreamValue
+        res = super().forward(ctx)
+        return res, StreamValue(self.norm.apply(res))
+
+
+register_part("embedding", "normed_embedding", NormedEmbedding)

@@ -57,3 +57,37 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", "swiglu", SwiGLU)
+
+
+class ClampedGLU(FeedForward):
+    """A gated feed-forward with clamps: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
+    output W_down (g sigmoid(slope g) (u + shift)).  gate and up are one product ([gate | up] by concatenation);
+    the activation is one kernel in float32; the last product leaves float32 for the stream's sum."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702, shift: float = 1.0):
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.limit, self.slope, self.shift = float(limit), float(slope), float(shift)
+
+    def tensor_specs(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {"gate": TensorSpec((i, h), "fan_in"), "up": TensorSpec((i, h), "fan_in"), "down": TensorSpec((h, i), "fan_in")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        g, u = tensors["gate"], tensors["up"]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = rt.place(torch.cat([g, u], 0))
+        self.w_down = rt.place(tensors["down"])
+
+    def kernel_sources(self):
+        return {"activation"} | self.rt.product_sources(self.w_gate_up, self.w_down)
+
+    def forward(self, x, ctx):
+        gu = self.rt.linear(x, self.w_gate_up)
+        act = self.rt.empty(x.shape[0], self.intermediate_size)
+        ops.glu_clamped(gu, act, self.limit, self.slope, self.shift)
+        return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGLU)

@@ -1,0 +1,51 @@
+"""Several mixers side by side on the same input: the result is the mean of their outputs, each first RMS-normed
+over the model width with a weight of its own.  The norms and the mean are not computed here: the mixer returns
+its branches (``Branches``) and the block's norm kernel takes them in, so the branch norms, the mean, the residual
+sum and the block's own norm are one launch.  What the branches need of the past is declared as a tuple; each
+branch gets its own ``LayerCache``."""
+from __future__ import annotations
+
+from ..weights.loader import TensorSpec
+from .base import Mixer, build_part, register_part
+from .block import Branches
+
+
+class ParallelMixers(Mixer):
+    def __init__(self, hidden_size: int, branches: dict):
+        """``branches``: {name: PartSpec of a mixer}; a branch's tensors are '<name>.<its own>', its out-norm weight
+        '<name>.out'."""
+        if not 1 <= len(branches) <= 2:
+            raise ValueError("the norm kernel adds one or two branches")
+        self.hidden_size = hidden_size
+        self.names = list(branches)
+        self.branches = [build_part("mixer", branches[n]) for n in self.names]
+
+    def tensor_specs(self):
+        specs = {}
+        for name, b in zip(self.names, self.branches):
+            specs.update({f"{name}.{k}": v for k, v in b.tensor_specs().items()})
+            specs[f"{name}.out"] = TensorSpec((self.hidden_size,), "normal:1:0.1")
+        return specs
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.out_weights = []
+        for name, b in zip(self.names, self.branches):
+            b.bind({k: tensors[f"{name}.{k}"] for k in b.tensor_specs()}, rt)
+            self.out_weights.append(rt.place(tensors[f"{name}.out"]))
+
+    def cache_need(self):
+        return tuple(b.cache_need() for b in self.branches)
+
+    def kernel_sources(self):
+        names = set()
+        for b in self.branches:
+            names |= b.kernel_sources()
+        return names
+
+    def forward(self, x, ctx, cache):
+        outs = [b.forward(x, ctx, c) for b, c in zip(self.branches, cache.parts)]
+        return Branches(outs, self.out_weights, coef=1.0 / len(outs))
+
+
+register_part("mixer", "parallel", ParallelMixers)

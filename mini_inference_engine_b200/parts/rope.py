@@ -89,3 +89,25 @@ class NoPosition(Rope):
 
 register_part("position", "rope", Rope)
 register_part("position", "none", NoPosition)
+
+
+def rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> torch.Tensor:
+    """float32 frequencies f_i = base^(-2i/dims), i < dims/2, for kernels that compute angles from positions
+    themselves (no table, no bound on the position).  ``scaling`` = {factor, low, high, original} rescales by
+    wavelength l = 2 pi / f: waves shorter than original/high keep their frequency, waves longer than
+    original/low get f / factor, and between the two the frequency is the blend (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low)."""
+    import math
+    out = []
+    for i in range(dims // 2):
+        f = float(base) ** (-2.0 * i / dims)
+        if scaling:
+            factor, low, high, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            wave = 2.0 * math.pi / f
+            if wave > orig / low:
+                f = f / factor
+            elif wave >= orig / high:
+                s = (orig / wave - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return torch.tensor(out, dtype=torch.float32)

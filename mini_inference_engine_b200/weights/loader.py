@@ -44,7 +44,8 @@ class WeightError(ValueError):
 class TensorSpec:
     """What a part expects of one checkpoint tensor."""
     shape: tuple
-    init: str = "normal"      # random-weights mode: "normal" (N(0, 0.02)), "ones" or "zeros"
+    init: str = "normal"      # random-weights mode: "normal" (N(0, 0.02)), "ones", "zeros", "fan_in" (N(0, 1 / last dimension)),
+                              # "normal:<mean>:<std>" or "uniform:<low>:<high>"
 
 
 def read_model_folder(path: str) -> dict[str, torch.Tensor]:
@@ -66,13 +67,16 @@ def storage_dtype(t: torch.Tensor) -> torch.dtype:
 
 
 def check_and_bind(state: dict[str, torch.Tensor], expected: dict[str, TensorSpec], *,
-                   ignore: tuple = (), where: str = "checkpoint") -> dict[str, torch.Tensor]:
-    """Returns ``{name: tensor}`` for exactly the expected names, each in its storage dtype."""
-    missing = [n for n in expected if n not in state]
-    unexpected = [n for n in state if n not in expected
+                   ignore: tuple = (), where: str = "checkpoint", aliases: dict | None = None) -> dict[str, torch.Tensor]:
+    """Returns ``{name: tensor}`` for exactly the expected names, each in its storage dtype.  ``aliases`` maps an
+    expected name to the name the checkpoint uses for it; the error lists the checkpoint's names."""
+    file_name = {n: (aliases or {}).get(n, n) for n in expected}
+    in_file = set(file_name.values())
+    missing = [f for f in file_name.values() if f not in state]
+    unexpected = [n for n in state if n not in in_file
                   and not any(fnmatch.fnmatchcase(n, pat) for pat in ignore)]
-    wrong = [(n, tuple(state[n].shape), tuple(s.shape)) for n, s in expected.items()
-             if n in state and tuple(state[n].shape) != tuple(s.shape)]
+    wrong = [(file_name[n], tuple(state[file_name[n]].shape), tuple(s.shape)) for n, s in expected.items()
+             if file_name[n] in state and tuple(state[file_name[n]].shape) != tuple(s.shape)]
     if missing or unexpected or wrong:
         raise WeightError(where, sorted(missing), sorted(unexpected), sorted(wrong))
-    return {n: state[n].to(storage_dtype(state[n])) for n in expected}
+    return {n: state[file_name[n]].to(storage_dtype(state[file_name[n]])) for n in expected}

@@ -29,10 +29,17 @@ def random_tensor(seed: int, name: str, spec: TensorSpec, dtype: torch.dtype) ->
         return torch.ones(spec.shape, dtype=dtype)
     if spec.init == "zeros":
         return torch.zeros(spec.shape, dtype=dtype)
-    if spec.init != "normal":
-        raise ValueError(f"unknown init {spec.init!r} for {name}")
     t = torch.empty(spec.shape, dtype=torch.float32)
-    t.normal_(0.0, INIT_STD, generator=_generator(seed, name))
+    kind, *args = spec.init.split(":")
+    if kind == "normal":
+        mean, std = (float(args[0]), float(args[1])) if args else (0.0, INIT_STD)
+        t.normal_(mean, std, generator=_generator(seed, name))
+    elif kind == "fan_in":
+        t.normal_(0.0, spec.shape[-1] ** -0.5, generator=_generator(seed, name))
+    elif kind == "uniform":
+        t.uniform_(float(args[0]), float(args[1]), generator=_generator(seed, name))
+    else:
+        raise ValueError(f"unknown init {spec.init!r} for {name}")
     return t.to(dtype)
 
 
@@ -47,6 +54,8 @@ def write_model_folder(path: str, config, seed: int, dtype: torch.dtype = torch.
     os.makedirs(path, exist_ok=True)
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(config.to_dict(), f, indent=1)
-    state = random_state(expected_tensors(config.model_spec()), seed, dtype)
+    spec = config.model_spec()
+    aliases = getattr(spec, "aliases", None) or {}
+    state = {aliases.get(n, n): t for n, t in random_state(expected_tensors(spec), seed, dtype).items()}
     write_file(os.path.join(path, "model.safetensors"), state, {"format": "pt", "seed": seed})
     return path
