@@ -383,6 +383,145 @@ def run_reference(args, steps, warmup):
                 f"(at {os.path.basename(last.filename)}:{last.lineno})".replace("\n", " ")}
 
 
+# --------------------------------------------------------------------------- another design beside Llama at equal size
+
+DESIGN_SIZES = {
+    # width, feed-forward, attention heads / key heads of 128, retention heads (keys of 128, values of 256), layers
+    "w2048": dict(width=2048, ff=5632, heads=16, kv_heads=4, ret_heads=8, layers=6),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, ret_heads=16, layers=6),
+}
+
+
+def design_configs(size: dict, vocab=32000, positions=4096):
+    """A Getizen configuration of the given layer sizes (one retention layer for every two parallel ones) and the Llama
+    configuration with the same width, feed-forward, heads and number of layers."""
+    from mini_inference_engine_b200.config import load_config
+    w, ff = size["width"], size["ff"]
+    mlp = dict(kind="dense", ff=ff, limit=7.0)
+    ret = dict(type="retention", mlp=mlp, mixer=dict(heads=size["ret_heads"], dim=128, vdim=256, rot=dict(base=1e4, dims=128),
+               decay=[1.0 - 2.0 ** (-5 - i % 8) for i in range(size["ret_heads"])]))
+    par = dict(type="parallel", mlp=mlp, mixer=dict(
+        left=dict(heads=size["heads"], kv_heads=size["kv_heads"], dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=positions),
+                  rot=dict(base=5e5, dims=128, scaling=dict(factor=8.0, low=1.0, high=4.0, original=positions))),
+        right=dict(width=w, blocks=w // 256, conv=4)))
+    layers = [ret if i % 3 == 0 else par for i in range(size["layers"])]
+    getizen = load_config(dict(architecture="Getizen", vocab=vocab, width=w, postln_alpha=1.0, norm=dict(eps=1e-5, groups=2),
+                               layers=layers))
+    llama = load_config(dict(architectures=["LlamaForCausalLM"], vocab_size=vocab, hidden_size=w, intermediate_size=ff,
+                             num_hidden_layers=size["layers"], num_attention_heads=size["heads"],
+                             num_key_value_heads=size["kv_heads"], head_dim=128, rms_norm_eps=1e-5, rope_theta=5e5,
+                             max_position_embeddings=positions, tie_word_embeddings=True))
+    return getizen, llama
+
+
+KERNEL_FACES = ("embedding", "add_rmsnorm", "stream_norm", "rope_cache_write", "qk_norm_rope", "paged_attention", "prefill_attention",
+                "prefill_attention_tc", "decode_attention", "retention_scan", "head_rms_gate", "causal_conv", "recurrence_gates",
+                "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate")
+
+
+class KernelTimes:
+    """Device time of every launch made through the package's kernel faces and its matrix products while active, by
+    name (events around each call on the launching stream; meant for runs with programmatic dependent launch off, so
+    that one kernel's time does not hide under its neighbour's)."""
+
+    def __init__(self):
+        self.records, self._saved = [], []
+
+    def _wrap(self, name, fn):
+        import torch
+
+        def timed(*a, **k):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*a, **k)
+            e.record()
+            self.records.append((name, s, e))
+            return out
+        return timed
+
+    def __enter__(self):
+        from mini_inference_engine_b200.kernels import linear, ops
+        for mod, names in ((ops, KERNEL_FACES), (linear, ("linear", "linear_swiglu", "linear_into_stream"))):
+            for n in names:
+                self._saved.append((mod, n, getattr(mod, n)))
+                setattr(mod, n, self._wrap(n, getattr(mod, n)))
+        return self
+
+    def __exit__(self, *exc):
+        for mod, n, fn in self._saved:
+            setattr(mod, n, fn)
+
+    def by_name(self):
+        import torch
+        torch.cuda.synchronize()
+        out = {}
+        for name, s, e in self.records:
+            t = out.setdefault(name, [0, 0.0])
+            t[0] += 1
+            t[1] += s.elapsed_time(e) * 1e3
+        self.records = []
+        return {k: {"launches": v[0], "us": round(v[1], 1)} for k, v in sorted(out.items())}
+
+
+def run_design(args, steps, warmup):
+    """Prefill and decode throughput of the Getizen design beside Llama at equal layer sizes (random weights), and with
+    ``--kernel-table`` the device time of every kernel of one prompt step and one decode step of both."""
+    import torch
+
+    from mini_inference_engine_b200 import EngineConfig, LLMEngine
+    from mini_inference_engine_b200.weights import write_model_folder
+    pk = peaks()
+    out = {"metric": "design_comparison", "design": "Getizen", "beside": "Llama", "dtype": "bf16", "data": "synthetic (random weights, seed 0)",
+           "peaks": pk, "sizes": {}}
+    batches = [int(b) for b in args.points.split(",") if b] or [8]
+    for size_name in args.sizes.split(","):
+        size = DESIGN_SIZES[size_name]
+        entry = out["sizes"][size_name] = {"layers": size["layers"]}
+        for label, cfg in zip(("getizen", "llama"), design_configs(size)):
+            folder = tempfile.mkdtemp(prefix="mie_b200_bench_")
+            try:
+                write_model_folder(folder, cfg, seed=0)
+                eng = LLMEngine(folder, EngineConfig(max_num_seqs=max(batches), max_num_batched_tokens=max(2048, args.prefill_tokens),
+                                                     max_model_len=4096, cuda_graph_batch_sizes=tuple(sorted(set(batches))),
+                                                     kv_cache_memory_fraction=0.3, use_cuda_graphs=not args.kernel_table),
+                                dtype=torch.bfloat16, load_tokenizer=False, verbose=False)
+            finally:
+                shutil.rmtree(folder, ignore_errors=True)
+            res = entry[label] = {"weight_bytes": eng.model.weight_bytes()}
+            if args.kernel_table:
+                from mini_inference_engine_b200 import SamplingParams
+                with KernelTimes() as kt:
+                    prefill_point(eng, args.prefill_tokens, 1, 2)
+                    kt.by_name()
+                    prefill_point(eng, args.prefill_tokens, 1, 0)
+                    res[f"prefill_{args.prefill_tokens}_kernels"] = kt.by_name()
+                    for p in prompts_for(batches[-1], args.context, eng.vocab_size):
+                        eng.add_request(p, SamplingParams(max_tokens=16, ignore_eos=True))
+                    while any(s.num_new_tokens > 1 for s in eng.scheduler.running) or eng.scheduler.waiting:
+                        eng.step()
+                    for _ in range(3):
+                        eng.step()
+                    eng.drain()
+                    kt.by_name()
+                    eng.step()
+                    eng.drain()
+                    res[f"decode_b{batches[-1]}_kernels"] = kt.by_name()
+                    for s in list(eng.scheduler.running):
+                        eng.scheduler.finish(s)
+            else:
+                pre_ms = prefill_point(eng, args.prefill_tokens, max(3, min(10, steps // 10)), 3)
+                res["prefill_tokens_per_s"] = round(args.prefill_tokens / pre_ms * 1e3, 1)
+                res["prefill_ms"] = round(pre_ms, 3)
+                for b in batches:
+                    pt = decode_point(eng, b, args.context, max(10, steps // 2), warmup)
+                    res[f"decode_b{b}_tokens_per_s"] = round(b / pt["device_ms"] * 1e3, 1)
+                    res[f"decode_b{b}_ms"] = round(pt["device_ms"], 4)
+                    res[f"decode_b{b}_launches"] = pt["launches_per_step"]
+            del eng
+            torch.cuda.empty_cache()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -395,8 +534,20 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--preset", default="tinyllama-1.1b")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--design", default=None, choices=["getizen"],
+                    help="instead of the default workload: prefill and decode throughput of this design beside Llama at equal "
+                         "layer sizes (--sizes), random weights; decode batches from --points")
+    ap.add_argument("--sizes", default="w2048,w4096", help="with --design: layer sizes to measure, of " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="with --design: device time of every kernel of one prompt step and one decode step (run with MIE_B200_PDL=0)")
     args = ap.parse_args()
 
+    if args.design:
+        if args.gpus != 1:
+            print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+            return 2
+        print(json.dumps(run_design(args, max(1, args.steps), max(3, args.warmup))))
+        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

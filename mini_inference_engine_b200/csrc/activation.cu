@@ -102,12 +102,45 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
     }
 }
 
+// Eight outputs a thread with 16-byte accesses (bfloat16, inter % 8 == 0)
+__global__ void glu_clamped_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int inter8,
+                                          float limit, float slope, float shift) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / inter8;
+        const int i8 = (int)(idx - t * inter8);
+        const bf16* row = gu + t * 16 * inter8;
+        const uint4 a = *reinterpret_cast<const uint4*>(row + 8 * i8), b = *reinterpret_cast<const uint4*>(row + 8 * inter8 + 8 * i8);
+        const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float2 g = __bfloat1622float2(ha[j]), u = __bfloat1622float2(hb[j]);
+            if (limit > 0.f) {
+                g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+                u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+            }
+            ho[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-slope * g.x)) * (u.x + shift),
+                                          __fdividef(g.y, 1.0f + __expf(-slope * g.y)) * (u.y + shift));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = o;
+    }
+}
+
 extern "C" int mie_glu_clamped(const void* gu, void* out, int act_tag, int num_tokens, int inter, float limit, float slope,
                                float shift, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (inter <= 0) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)num_tokens * inter;
     const int threads = 256;
+    if (act_tag == MIE_BF16 && inter % 8 == 0 && (reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        int64_t blocks8 = (total / 8 + threads - 1) / threads;
+        if (blocks8 > device_sm_count() * 16) blocks8 = device_sm_count() * 16;
+        return launch_kernel(glu_clamped_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out,
+                             total / 8, inter / 8, limit, slope, shift);
+    }
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (act_tag == MIE_F32)
@@ -135,12 +168,42 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ attn, const T* __restr
     }
 }
 
+__global__ void sigmoid_gate_bf16x8_kernel(const bf16* __restrict__ attn, const bf16* __restrict__ g, int64_t g_stride,
+                                           bf16* __restrict__ out, int64_t total8, int H, int Dv8, int DP) {
+    pdl_enter();
+    const int n8 = H * Dv8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / n8;
+        const int i8 = (int)(idx - t * n8);
+        const int h = i8 / Dv8, c8 = i8 - h * Dv8;
+        const uint4 a = *reinterpret_cast<const uint4*>(attn + (t * H + h) * DP + 8 * c8);
+        const uint4 z = *reinterpret_cast<const uint4*>(g + t * g_stride + 8 * i8);
+        const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* hz = reinterpret_cast<const __nv_bfloat162*>(&z);
+        uint4 o;
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 x = __bfloat1622float2(ha[j]), y = __bfloat1622float2(hz[j]);
+            ho[j] = __floats2bfloat162_rn(__fdividef(x.x, 1.0f + __expf(-y.x)), __fdividef(x.y, 1.0f + __expf(-y.y)));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = o;
+    }
+}
+
 extern "C" int mie_sigmoid_gate(const void* attn, const void* g, long long g_stride, void* out, int act_tag, int num_tokens,
                                 int H, int Dv, int DP, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (H <= 0 || Dv <= 0 || DP < Dv) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)num_tokens * H * Dv;
     const int threads = 256;
+    if (act_tag == MIE_BF16 && Dv % 8 == 0 && DP % 8 == 0 && g_stride % 8 == 0 &&
+        (reinterpret_cast<uintptr_t>(attn) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        int64_t blocks8 = (total / 8 + threads - 1) / threads;
+        if (blocks8 > device_sm_count() * 16) blocks8 = device_sm_count() * 16;
+        return launch_kernel(sigmoid_gate_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)attn, (const bf16*)g,
+                             (int64_t)g_stride, (bf16*)out, total / 8, H, Dv / 8, DP);
+    }
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (act_tag == MIE_F32)

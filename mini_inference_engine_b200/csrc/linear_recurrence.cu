@@ -9,81 +9,113 @@
 // request the unit keeps `state[slot]` = [K rows, C] float32: row 0 is s, rows 1 .. K-1 are the last K-1 inputs x
 // of the convolution (oldest first).  Three launches:
 //   conv      every (token, channel) on its own: inputs older than the portion come from the state
-//   gates     a block of threads takes GATE_TT tokens of one channel block: u in shared memory, one output channel a
-//             thread, both gate matrices in one pass; writes a_t and the gated input sqrt(1 - a_t^2) i_t u_t
+//   gates     both block-diagonal gate matrices in one tiled float32 product on CUDA cores (weights read as float32);
+//             writes a_t and the gated input sqrt(1 - a_t^2) i_t u_t
 //   scan      a request's tokens are cut into segments; every (segment, channel) thread first folds its segment
 //             into (product of a, value from zero), the segments' starts follow from those in order, then each
 //             segment is walked again from its start; the last one stores s, and the convolution's inputs move on
 #include "common.cuh"
 
-#define CONV_MAX_TAPS 16
-#define GATE_TT 16
+#define CONV_MAX_TAPS 8
 
+#define CONV_TOKENS 8         // consecutive tokens a thread computes (their inputs overlap and come from the L1 cache)
 template <typename T>
 __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t x_stride, const int* __restrict__ token_row,
                                    const int* __restrict__ row_q_start, const int* __restrict__ state_slots,
-                                   const void* __restrict__ taps, const void* __restrict__ bias, int w_tag,
+                                   const float* __restrict__ taps, const float* __restrict__ bias,
                                    const float* __restrict__ state, float* __restrict__ u, int num_tokens, int C, int K) {
     pdl_enter();
-    const int t = blockIdx.y;
     const int ch = blockIdx.x * blockDim.x + threadIdx.x;
-    if (ch >= C || t >= num_tokens) return;
-    const int r = token_row[t];
-    const int lt = t - row_q_start[r];                       // index within the request's portion
-    const float* hist = state + (int64_t)state_slots[r] * K * C + C;      // rows 1 .. K-1
-    float acc = bias ? load_tagged(bias, ch, w_tag) : 0.f;
-    for (int j = 0; j < K; ++j) {
-        const int src = lt - (K - 1) + j;
-        const float xv = src >= 0 ? to_f32<T>(x[(int64_t)(t - (K - 1) + j) * x_stride + ch])
-                                  : hist[(int64_t)(src + K - 1) * C + ch];
-        acc = fmaf(load_tagged(taps, (int64_t)ch * K + j, w_tag), xv, acc);
-    }
-    u[(int64_t)t * C + ch] = acc;
-}
-
-__global__ void recurrence_gates_kernel(const float* __restrict__ u, const void* __restrict__ wa, const void* __restrict__ ba,
-                                        const void* __restrict__ wi, const void* __restrict__ bi, const void* __restrict__ lam,
-                                        int w_tag, float c_exp, float* __restrict__ a_out, float* __restrict__ b_out,
-                                        int num_tokens, int C, int bw) {
-    extern __shared__ float u_s[];                           // [GATE_TT][bw]
-    pdl_enter();
-    const int blk = blockIdx.y;
-    const int t0 = blockIdx.x * GATE_TT;
-    const int nt = min(GATE_TT, num_tokens - t0);
-    for (int i = threadIdx.x; i < GATE_TT * bw; i += blockDim.x) {
-        const int tt = i / bw, k = i - tt * bw;
-        u_s[i] = tt < nt ? u[(int64_t)(t0 + tt) * C + blk * bw + k] : 0.f;
-    }
-    __syncthreads();
-    for (int o = threadIdx.x; o < bw; o += blockDim.x) {
-        float ra[GATE_TT], ri[GATE_TT];
+    if (ch >= C) return;
+    float w[CONV_MAX_TAPS];
 #pragma unroll
-        for (int tt = 0; tt < GATE_TT; ++tt) { ra[tt] = 0.f; ri[tt] = 0.f; }
-        const int64_t wrow = ((int64_t)blk * bw + o) * bw;
-        for (int k = 0; k < bw; ++k) {
-            const float a = load_tagged(wa, wrow + k, w_tag), b = load_tagged(wi, wrow + k, w_tag);
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < K ? taps[(int64_t)ch * K + j] : 0.f;
+    const float cb = bias ? bias[ch] : 0.f;
+    const int t_end = min(num_tokens, (int)(blockIdx.y + 1) * CONV_TOKENS);
+    for (int t = blockIdx.y * CONV_TOKENS; t < t_end; ++t) {
+        const int r = token_row[t];
+        const int lt = t - row_q_start[r];                       // index within the request's portion
+        const float* hist = state + (int64_t)state_slots[r] * K * C + C;      // rows 1 .. K-1
+        float acc = cb;
 #pragma unroll
-            for (int tt = 0; tt < GATE_TT; ++tt) {
-                const float uv = u_s[tt * bw + k];
-                ra[tt] = fmaf(a, uv, ra[tt]);
-                ri[tt] = fmaf(b, uv, ri[tt]);
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < K) {
+                const int src = lt - (K - 1) + j;
+                const float xv = src >= 0 ? to_f32<T>(x[(int64_t)(t - (K - 1) + j) * x_stride + ch])
+                                          : hist[(int64_t)(src + K - 1) * C + ch];
+                acc = fmaf(w[j], xv, acc);
             }
         }
+        u[(int64_t)t * C + ch] = acc;
+    }
+}
+
+// A tile of GATE_TM tokens x GATE_TN output channels of one channel block per thread block (16 x 16 threads, 4 x 4
+// outputs of both gate matrices a thread); u and both weight tiles go through shared memory GATE_TK input channels at
+// a time, transposed so that a thread reads its four tokens and its four channels as one float4 each.
+#define GATE_TM 64
+#define GATE_TN 64
+#define GATE_TK 16
+__global__ void __launch_bounds__(256) recurrence_gates_kernel(
+        const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba, const float* __restrict__ wi,
+        const float* __restrict__ bi, const float* __restrict__ lam, float c_exp, float* __restrict__ a_out,
+        float* __restrict__ b_out, int num_tokens, int C, int bw, int n_tiles) {
+    __shared__ __align__(16) float u_s[GATE_TK][GATE_TM + 4];
+    __shared__ __align__(16) float wa_s[GATE_TK][GATE_TN + 4];
+    __shared__ __align__(16) float wi_s[GATE_TK][GATE_TN + 4];
+    pdl_enter();
+    const int blk = blockIdx.y / n_tiles, o0 = (blockIdx.y - blk * n_tiles) * GATE_TN;
+    const int t0 = blockIdx.x * GATE_TM;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // tx: outputs 4 tx .. 4 tx + 3, ty: tokens 4 ty .. 4 ty + 3
+    float ra[4][4], ri[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { ra[i][j] = 0.f; ri[i][j] = 0.f; }
+    for (int k0 = 0; k0 < bw; k0 += GATE_TK) {
+        __syncthreads();
+        for (int i = threadIdx.x; i < GATE_TM * GATE_TK; i += 256) {
+            const int row = i / GATE_TK, kk = i - row * GATE_TK;      // row: a token or an output channel
+            const bool k_ok = k0 + kk < bw;
+            u_s[kk][row] = (k_ok && t0 + row < num_tokens) ? u[(int64_t)(t0 + row) * C + blk * bw + k0 + kk] : 0.f;
+            const bool w_ok = k_ok && o0 + row < bw;
+            const int64_t w = ((int64_t)blk * bw + o0 + row) * bw + k0 + kk;
+            wa_s[kk][row] = w_ok ? wa[w] : 0.f;
+            wi_s[kk][row] = w_ok ? wi[w] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GATE_TK; ++kk) {
+            const float4 uv = *reinterpret_cast<const float4*>(&u_s[kk][4 * ty]);
+            const float4 av = *reinterpret_cast<const float4*>(&wa_s[kk][4 * tx]);
+            const float4 iv = *reinterpret_cast<const float4*>(&wi_s[kk][4 * tx]);
+            const float uu[4] = {uv.x, uv.y, uv.z, uv.w}, aa[4] = {av.x, av.y, av.z, av.w}, ii[4] = {iv.x, iv.y, iv.z, iv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    ra[i][j] = fmaf(uu[i], aa[j], ra[i][j]);
+                    ri[i][j] = fmaf(uu[i], ii[j], ri[i][j]);
+                }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int o = o0 + 4 * tx + j;
+        if (o >= bw) continue;
         const int ch = blk * bw + o;
-        const float bra = load_tagged(ba, ch, w_tag), bri = load_tagged(bi, ch, w_tag);
-        const float l = load_tagged(lam, ch, w_tag);
+        const float bra = ba[ch], bri = bi[ch], l = lam[ch];
         const float sp = l > 20.f ? l : log1pf(expf(l));                  // softplus
 #pragma unroll
-        for (int tt = 0; tt < GATE_TT; ++tt) {
-            if (tt < nt) {
-                const float r = 1.0f / (1.0f + expf(-(ra[tt] + bra)));
-                const float g = 1.0f / (1.0f + expf(-(ri[tt] + bri)));
-                const float la = -c_exp * r * sp;
-                const float a = expf(la);
-                const float m = sqrtf(fmaxf(1.0f - a * a, 0.f));
-                a_out[(int64_t)(t0 + tt) * C + ch] = a;
-                b_out[(int64_t)(t0 + tt) * C + ch] = m * (g * u_s[tt * bw + o]);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const int t = t0 + 4 * ty + i;
+            if (t >= num_tokens) continue;
+            const float r = 1.0f / (1.0f + expf(-(ra[i][j] + bra)));
+            const float g = 1.0f / (1.0f + expf(-(ri[i][j] + bri)));
+            const float a = expf(-c_exp * r * sp);
+            const float m = sqrtf(fmaxf(1.0f - a * a, 0.f));
+            a_out[(int64_t)t * C + ch] = a;
+            b_out[(int64_t)t * C + ch] = m * (g * u[(int64_t)t * C + ch]);
         }
     }
 }
@@ -115,6 +147,7 @@ __global__ void recurrence_scan_kernel(const float* __restrict__ a, const float*
     if (nseg > 1) {
         float A = 1.f, Bv = 0.f;
         if (ok)
+#pragma unroll 8
             for (int t = lo; t < hi; ++t) {
                 const int64_t i = (int64_t)(q_start + t) * C + ch;
                 const float at = a[i];
@@ -127,6 +160,7 @@ __global__ void recurrence_scan_kernel(const float* __restrict__ a, const float*
     }
     if (!ok) return;
     for (int k = 0; k < seg; ++k) s = fmaf(A_s[k * 32 + threadIdx.x], s, B_s[k * 32 + threadIdx.x]);
+#pragma unroll 8
     for (int t = lo; t < hi; ++t) {
         const int64_t i = (int64_t)(q_start + t) * C + ch;
         s = fmaf(a[i], s, b[i]);
@@ -150,34 +184,31 @@ __global__ void recurrence_scan_kernel(const float* __restrict__ a, const float*
 }
 
 extern "C" int mie_causal_conv(const void* x, int tag, long long x_stride, const int* token_row, const int* row_q_start,
-                               const int* state_slots, const void* taps, const void* bias, int w_tag, const float* state,
+                               const int* state_slots, const float* taps, const float* bias, const float* state,
                                float* u, int num_tokens, int C, int K, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (C <= 0 || K < 1 || K > CONV_MAX_TAPS) return MIE_ERR_BAD_ARG;
     const int threads = 128;
-    dim3 grid((C + threads - 1) / threads, num_tokens);
+    dim3 grid((C + threads - 1) / threads, (num_tokens + CONV_TOKENS - 1) / CONV_TOKENS);
     if (tag == MIE_F32)
         return launch_kernel(causal_conv_kernel<float>, grid, dim3(threads), 0, stream, (const float*)x, (int64_t)x_stride, token_row,
-                             row_q_start, state_slots, taps, bias, w_tag, state, u, num_tokens, C, K);
+                             row_q_start, state_slots, taps, bias, state, u, num_tokens, C, K);
     else if (tag == MIE_BF16)
         return launch_kernel(causal_conv_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)x, (int64_t)x_stride, token_row,
-                             row_q_start, state_slots, taps, bias, w_tag, state, u, num_tokens, C, K);
+                             row_q_start, state_slots, taps, bias, state, u, num_tokens, C, K);
     return MIE_ERR_BAD_ARG;
 }
 
-extern "C" int mie_recurrence_gates(const float* u, const void* wa, const void* ba, const void* wi, const void* bi,
-                                    const void* lam, int w_tag, float c_exp, float* a_out, float* b_out, int num_tokens,
+extern "C" int mie_recurrence_gates(const float* u, const float* wa, const float* ba, const float* wi, const float* bi,
+                                    const float* lam, float c_exp, float* a_out, float* b_out, int num_tokens,
                                     int C, int blocks, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (C <= 0 || blocks <= 0 || C % blocks) return MIE_ERR_BAD_ARG;
     const int bw = C / blocks;
-    const size_t smem = (size_t)GATE_TT * bw * sizeof(float);
-    if (smem > 96 * 1024) return MIE_ERR_TOO_LARGE;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(recurrence_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    const int threads = bw >= 256 ? 256 : (bw + 31) / 32 * 32;
-    dim3 grid((num_tokens + GATE_TT - 1) / GATE_TT, blocks);
-    return launch_kernel(recurrence_gates_kernel, grid, dim3(threads), smem, stream, u, wa, ba, wi, bi, lam, w_tag, c_exp, a_out,
-                         b_out, num_tokens, C, bw);
+    const int n_tiles = (bw + GATE_TN - 1) / GATE_TN;
+    dim3 grid((num_tokens + GATE_TM - 1) / GATE_TM, blocks * n_tiles);
+    return launch_kernel(recurrence_gates_kernel, grid, dim3(256), 0, stream, u, wa, ba, wi, bi, lam, c_exp, a_out, b_out,
+                         num_tokens, C, bw, n_tiles);
 }
 
 extern "C" int mie_recurrence_scan(const float* a, const float* b, const void* y, int tag, long long y_stride, const void* x,

@@ -11,7 +11,8 @@
 //   every head is zero, so that kernels written for one head size serve heads whose key and value sizes differ.
 //
 // `freq` holds rot/2 float32 frequencies (the host computes them, with whatever rescaling the model asks for);
-// angles, cosines and sines are float32 and computed here from the position, so no table bounds the positions.
+// angles, cosines and sines are float32 and computed here from the position (once per token, for all heads), so no
+// table bounds the positions.
 // Statistics and all arithmetic are float32; outputs are rounded to the activation type once.  One block per token.
 #include "common.cuh"
 #include "range_check.cuh"
@@ -26,6 +27,7 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int64_t qkv_strid
                                     T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int G, int D, int Dv, int DP,
                                     int rot, int page_size, int64_t num_pages, int write_cache, int* report) {
     __shared__ float red[33];
+    extern __shared__ float cs[];                 // cos [rot/2], sin [rot/2]: once per token, for all heads
     pdl_enter();
     const int t = blockIdx.x;
     const T* q = qkv + (int64_t)t * qkv_stride;
@@ -44,6 +46,12 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int64_t qkv_strid
         sk = 1.0f / sqrtf(block_sum(ss, red) / (float)(G * D) + eps);
     }
     const int half = rot >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float a = pos * freq[i];
+        cs[i] = cosf(a);
+        cs[half + i] = sinf(a);
+    }
+    __syncthreads();
     // one entry of a rotated projection: x normed, then turned with its partner
     auto entry = [&](const T* x, const void* w, float s, int h, int d) -> float {
         float own = to_f32<T>(x[h * D + d]) * s;
@@ -52,8 +60,7 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int64_t qkv_strid
         const int pd = d < half ? d + half : d - half;
         float other = to_f32<T>(x[h * D + pd]) * s;
         if (w) other *= load_tagged(w, h * D + pd, w_tag);
-        const float a = pos * freq[d < half ? d : d - half];
-        const float c = cosf(a), sn = sinf(a);
+        const float c = cs[d < half ? d : d - half], sn = cs[half + (d < half ? d : d - half)];
         return d < half ? own * c - other * sn : own * c + other * sn;
     };
     T* qo = q_out + (int64_t)t * H * DP;
@@ -91,12 +98,12 @@ extern "C" int mie_qk_norm_rope(const void* qkv, int tag, long long qkv_stride, 
         return MIE_ERR_BAD_ARG;
     const int threads = H * DP >= 2048 ? 256 : 128;
     if (tag == MIE_F32)
-        return launch_kernel(qk_norm_rope_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)qkv,
+        return launch_kernel(qk_norm_rope_kernel<float>, dim3(num_tokens), dim3(threads), (size_t)rot * sizeof(float), stream, (const float*)qkv,
                              (int64_t)qkv_stride, positions, slots, freq, qw, kw, temp, w_tag, eps, q_scale, k_scale,
                              (float*)q_out, (float*)k_cache, (float*)v_cache, H, G, D, Dv, DP, rot, page_size,
                              (int64_t)num_pages, write_cache, g_range_report);
     else if (tag == MIE_BF16)
-        return launch_kernel(qk_norm_rope_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)qkv,
+        return launch_kernel(qk_norm_rope_kernel<bf16>, dim3(num_tokens), dim3(threads), (size_t)rot * sizeof(float), stream, (const bf16*)qkv,
                              (int64_t)qkv_stride, positions, slots, freq, qw, kw, temp, w_tag, eps, q_scale, k_scale,
                              (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, H, G, D, Dv, DP, rot, page_size,
                              (int64_t)num_pages, write_cache, g_range_report);

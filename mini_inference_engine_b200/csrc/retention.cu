@@ -1,74 +1,149 @@
 // Linear attention with a fixed decay per head and no softmax or denominator, as a recurrence over a
-// float32 state per request and head (prompt portions and single tokens through the same kernel):
+// float32 state per request and head (prompt portions and single tokens through the same kernels):
 //
 //   S_t = gamma_h * S_{t-1} + k_t v_t^T        S: [D, Dv],  S before a request's first token is zero
 //   o_t = S_t^T q_t
 //
-// q and k are read from the fused projection [ q: H x D | k: H x D | v: H x Dv | ... ] and rotated here
-// (rotate-half pairing over the first `rot` dims, angle = position * freq[i], float32), k is multiplied by
-// `k_scale` after the rotation.  The state lives in `state[slot, h, c, d]` (value column c, key dimension d:
-// transposed, so that the threads that share a column read neighbouring words).
+// q and k come from the fused projection [ q: H x D | k: H x D | v: H x Dv | ... ], are rotated (rotate-half pairing
+// over the first `rot` dims, angle = position * freq[i], float32) and k is multiplied by `k_scale` after the
+// rotation: the `prepare` kernel, one block per token, writes both as float32 [T, H, D]; a token's cosines and sines
+// are computed once and serve all heads.  The state lives in `state[slot, h, c, d]` (value column c, key dimension
+// d: transposed, so that the threads that share a column read neighbouring words).
 //
-// Work split: one block = one request, one head and a slice of value columns.  A column's state is held in the
-// registers of P threads of one warp (thread p holds the key dimensions p, p + P, p + 2P, ...: up to RET_DPT of
+// A request's new tokens are cut into chunks of RET_L.  The recurrence is linear in S, so a chunk's effect on the
+// state is (gamma^len, the state it builds from zero), and the chunks of a long portion run side by side:
+//   pass 0   every chunk j but the last of a row of two or more: the state it builds from zero     -> scratch[j + 1]
+//   combine  per such row, in order: scratch[0] = the request's state, scratch[j + 1] += gamma^RET_L * scratch[j]
+//   pass 1   every chunk from its start (scratch[j]; the request's state for a row of one chunk): outputs; a row's
+//            last chunk stores the state (no block reads the state of a row whose other blocks may write it)
+// A step whose rows all fit one chunk (decoding) runs pass 1 only.  Blocks find their (row, chunk) from the rows'
+// lengths on the device, so the launch is laid out for the step's token count, not for what the host knows of its rows.
+//
+// Work split of a pass: one block = one chunk, one head and a slice of value columns.  A column's state is held in
+// the registers of P threads of one warp (thread p holds the key dimensions p, p + P, p + 2P, ...: up to RET_DPT of
 // them), which add up their parts of o_t by shuffles.  Tokens are staged in shared memory RET_TT at a time.
 // Everything is float32.
 //
-// The second kernel finishes the mixer's head stage: every head's o is divided by its root mean square (no
+// The last kernel finishes the mixer's head stage: every head's o is divided by its root mean square (no
 // weight) and multiplied by silu(g), g being another part of the fused projection.
 #include "common.cuh"
 
 #define RET_DPT 16      // key dimensions per thread
-#define RET_TT 8        // tokens staged at a time
+#define RET_TT 16       // tokens staged at a time
+#define RET_L 64        // tokens per chunk
 
 template <typename T>
-__global__ void retention_scan_kernel(const T* __restrict__ qkv, int64_t stride, const int* __restrict__ row_q_start,
-                                      const int* __restrict__ row_q_len, const int* __restrict__ row_ctx_len,
-                                      const int* __restrict__ state_slots, const float* __restrict__ decay,
-                                      const float* __restrict__ freq, float k_scale, float* __restrict__ state,
-                                      float* __restrict__ out, int H, int D, int Dv, int rot, int P, int CW, int slices) {
+__global__ void retention_prepare_kernel(const T* __restrict__ qkv, int64_t stride, const int* __restrict__ positions,
+                                         const float* __restrict__ freq, float k_scale, float* __restrict__ qr,
+                                         float* __restrict__ kr, int H, int D, int rot) {
+    extern __shared__ float cs[];                 // cos [rot/2], sin [rot/2]
+    pdl_enter();
+    const int t = blockIdx.x, half = rot >> 1;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float a = pos * freq[i];
+        cs[i] = cosf(a);
+        cs[half + i] = sinf(a);
+    }
+    __syncthreads();
+    const T* src = qkv + (int64_t)t * stride;
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+        const int d = i % D;
+        float qo = to_f32<T>(src[i]), ko = to_f32<T>(src[H * D + i]);
+        if (d < rot) {
+            const int j = d < half ? d : d - half;
+            const int pi = d < half ? i + half : i - half;
+            const float c = cs[j], sn = cs[half + j];
+            const float qp = to_f32<T>(src[pi]), kp = to_f32<T>(src[H * D + pi]);
+            qo = d < half ? qo * c - qp * sn : qo * c + qp * sn;
+            ko = d < half ? ko * c - kp * sn : ko * c + kp * sn;
+        }
+        qr[(int64_t)t * H * D + i] = qo;
+        kr[(int64_t)t * H * D + i] = ko * k_scale;
+    }
+}
+
+// Which (row, chunk) has number `index`, counting every row's chunks (numbering 1: max(1, ceil(len / RET_L)) a row) or
+// only the chunks of rows that have two or more (numbering 0: these have a scratch slot each).  Returns the row (-1: none), the chunk within the row, the row's
+// count in that numbering, and how many chunks of numbering 0 lie in front of the row.  Asked by whole warps.
+__device__ __forceinline__ int find_chunk(const int* __restrict__ row_q_len, int num_rows, int index, int numbering,
+                                          int& within, int& items, int& before0) {
+    const int lane = threadIdx.x & 31;
+    int seen0 = 0;
+    for (int base = 0; base < num_rows; base += 32) {
+        const int r = base + lane;
+        const int n1 = r < num_rows ? max(1, (row_q_len[r] + RET_L - 1) / RET_L) : 0;
+        const int n0 = n1 > 1 ? n1 : 0;
+        const int n = numbering ? n1 : n0;
+        int incl = n, incl0 = n0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o), up0 = __shfl_up_sync(0xffffffffu, incl0, o);
+            if (lane >= o) { incl += up; incl0 += up0; }
+        }
+        const int total = __shfl_sync(0xffffffffu, incl, 31), total0 = __shfl_sync(0xffffffffu, incl0, 31);
+        if (index < total) {
+            const int l = __ffs(__ballot_sync(0xffffffffu, incl > index)) - 1;
+            items = __shfl_sync(0xffffffffu, n, l);
+            within = index - (__shfl_sync(0xffffffffu, incl, l) - items);
+            before0 = seen0 + __shfl_sync(0xffffffffu, incl0, l) - __shfl_sync(0xffffffffu, n0, l);
+            return base + l;
+        }
+        index -= total;
+        seen0 += total0;
+    }
+    within = 0; items = 0; before0 = 0;
+    return -1;
+}
+
+template <typename T, int PASS>
+__global__ void retention_chunk_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v,
+                                       int64_t v_stride, const int* __restrict__ row_q_start,
+                                       const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
+                                       const float* __restrict__ decay, float* __restrict__ state,
+                                       float* __restrict__ scratch, float* __restrict__ out, int num_rows, int H, int D, int Dv,
+                                       int P, int CW, int slices) {
     extern __shared__ float smem[];
     float* q_s = smem;                       // [RET_TT][D]
     float* k_s = q_s + RET_TT * D;           // [RET_TT][D]
     float* v_s = k_s + RET_TT * D;           // [RET_TT][CW]
     pdl_enter();
-    const int r = blockIdx.y;
+    int within, items, before0;
+    const int r = find_chunk(row_q_len, num_rows, (int)blockIdx.y, PASS, within, items, before0);
+    if (r < 0 || (PASS == 0 && within == items - 1)) return;          // nobody needs what a row's last chunk builds from zero
     const int h = blockIdx.x / slices, slice = blockIdx.x - h * slices;
-    const int q_len = row_q_len[r], q_start = row_q_start[r], pos0 = row_ctx_len[r] - q_len;
+    const int q_len = row_q_len[r], q_start = row_q_start[r];
+    const int t_lo = within * RET_L, t_hi = min(q_len, t_lo + RET_L);
     const int p = threadIdx.x % P, cl = threadIdx.x / P;
     const int c = slice * CW + cl;                                  // this thread's value column
     const bool col_ok = cl < CW && c < Dv;
     const float gamma = decay[h];
-    const int half = rot >> 1;
-    float* st = state + (((int64_t)state_slots[r] * H + h) * Dv + (col_ok ? c : 0)) * D;
+    const int64_t hcol = ((int64_t)h * Dv + (col_ok ? c : 0)) * D;
+    const int64_t per_state = (int64_t)H * Dv * D;
+    float* st = state + (int64_t)state_slots[r] * per_state + hcol;
     float S[RET_DPT];
+    {
+        // pass 0 builds from zero; pass 1 starts from the request's state or from what the combine left for this chunk
+        const float* from = PASS == 0 ? nullptr : (items == 1 ? st : scratch + (int64_t)(before0 + within) * per_state + hcol);
 #pragma unroll
-    for (int j = 0; j < RET_DPT; ++j) {
-        const int d = p + P * j;
-        S[j] = (col_ok && d < D) ? st[d] : 0.f;
+        for (int j = 0; j < RET_DPT; ++j) {
+            const int d = p + P * j;
+            S[j] = (from && col_ok && d < D) ? from[d] : 0.f;
+        }
     }
-    for (int t0 = 0; t0 < q_len; t0 += RET_TT) {
-        const int nt = min(RET_TT, q_len - t0);
+    for (int t0 = t_lo; t0 < t_hi; t0 += RET_TT) {
+        const int nt = min(RET_TT, t_hi - t0);
         __syncthreads();
+        const int64_t row0 = ((int64_t)(q_start + t0) * H + h) * D;
         for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
             const int tt = i / D, d = i - tt * D;
-            const T* src = qkv + (int64_t)(q_start + t0 + tt) * stride + h * D;
-            float qo = to_f32<T>(src[d]), ko = to_f32<T>(src[H * D + d]);
-            if (d < rot) {
-                const int pd = d < half ? d + half : d - half;
-                const float a = (float)(pos0 + t0 + tt) * freq[d < half ? d : d - half];
-                const float cs = cosf(a), sn = sinf(a);
-                const float qp = to_f32<T>(src[pd]), kp = to_f32<T>(src[H * D + pd]);
-                qo = d < half ? qo * cs - qp * sn : qo * cs + qp * sn;
-                ko = d < half ? ko * cs - kp * sn : ko * cs + kp * sn;
-            }
-            q_s[tt * D + d] = qo;
-            k_s[tt * D + d] = ko * k_scale;
+            k_s[i] = kr[row0 + (int64_t)tt * H * D + d];
+            if (PASS) q_s[i] = qr[row0 + (int64_t)tt * H * D + d];
         }
         for (int i = threadIdx.x; i < nt * CW; i += blockDim.x) {
             const int tt = i / CW, cc = i - tt * CW;
             const int col = slice * CW + cc;
-            v_s[tt * CW + cc] = col < Dv ? to_f32<T>(qkv[(int64_t)(q_start + t0 + tt) * stride + 2 * H * D + h * Dv + col]) : 0.f;
+            v_s[i] = col < Dv ? to_f32<T>(v[(int64_t)(q_start + t0 + tt) * v_stride + h * Dv + col]) : 0.f;
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -79,18 +154,43 @@ __global__ void retention_scan_kernel(const T* __restrict__ qkv, int64_t stride,
                 const int d = p + P * j;
                 if (d < D) {
                     S[j] = fmaf(gamma, S[j], k_s[tt * D + d] * vv);
-                    acc = fmaf(S[j], q_s[tt * D + d], acc);
+                    if (PASS) acc = fmaf(S[j], q_s[tt * D + d], acc);
                 }
             }
-            for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (p == 0 && col_ok) out[(int64_t)(q_start + t0 + tt) * H * Dv + h * Dv + c] = acc;
+            if (PASS) {
+                for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (p == 0 && col_ok) out[(int64_t)(q_start + t0 + tt) * H * Dv + h * Dv + c] = acc;
+            }
         }
     }
-    if (col_ok) {
+    float* to = PASS == 0 ? scratch + (int64_t)(before0 + within + 1) * per_state + hcol : (within == items - 1 ? st : nullptr);
+    if (to && col_ok) {
 #pragma unroll
         for (int j = 0; j < RET_DPT; ++j) {
             const int d = p + P * j;
-            if (d < D) st[d] = S[j];
+            if (d < D) to[d] = S[j];
+        }
+    }
+}
+
+// scratch[j] becomes the state at the start of chunk j, for every row with two chunks or more
+__global__ void retention_combine_kernel(const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
+                                         const float* __restrict__ decay, const float* __restrict__ state,
+                                         float* __restrict__ scratch, int num_rows, int H, int Dv, int D) {
+    pdl_enter();
+    int within, items, before0;
+    const int r = find_chunk(row_q_len, num_rows, (int)blockIdx.y, 0, within, items, before0);
+    if (r < 0 || within != 0) return;                       // the block of a row's first chunk walks the whole row
+    const int64_t per_state = (int64_t)H * Dv * D;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < per_state; e += (int64_t)gridDim.x * blockDim.x) {
+        const int h = (int)(e / ((int64_t)Dv * D));
+        const float g = exp2f((float)RET_L * log2f(decay[h]));
+        float cur = state[(int64_t)state_slots[r] * per_state + e];
+        scratch[(int64_t)before0 * per_state + e] = cur;
+        for (int j = 1; j < items; ++j) {
+            float* slot = scratch + (int64_t)(before0 + j) * per_state + e;
+            cur = fmaf(g, cur, *slot);
+            *slot = cur;
         }
     }
 }
@@ -116,11 +216,12 @@ __global__ void head_rms_gate_kernel(const float* __restrict__ o, const T* __res
     }
 }
 
-extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, const int* row_q_start, const int* row_q_len,
-                                  const int* row_ctx_len, const int* state_slots, const float* decay, const float* freq,
-                                  float k_scale, float* state, float* out, int num_rows, int H, int D, int Dv, int rot,
+extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, const int* positions, const int* row_q_start,
+                                  const int* row_q_len, const int* state_slots, const float* decay, const float* freq,
+                                  float k_scale, float* state, float* qr, float* kr, float* scratch, long long scratch_chunks,
+                                  float* out, int num_tokens, int num_rows, int max_q_len, int H, int D, int Dv, int rot,
                                   cudaStream_t stream) {
-    if (num_rows <= 0) return 0;
+    if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (H <= 0 || D <= 0 || Dv <= 0 || rot < 0 || rot > D || (rot & 1)) return MIE_ERR_BAD_ARG;
     int P = 1;
     while (P * RET_DPT < D) P <<= 1;
@@ -130,15 +231,35 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
     const int slices = (Dv + CW - 1) / CW;
     const int threads = (CW * P + 31) / 32 * 32;
     const size_t smem = (size_t)RET_TT * (2 * D + CW) * sizeof(float);
-    dim3 grid(H * slices, num_rows);
-    if (tag == MIE_F32)
-        return launch_kernel(retention_scan_kernel<float>, grid, dim3(threads), smem, stream, (const float*)qkv, (int64_t)stride,
-                             row_q_start, row_q_len, row_ctx_len, state_slots, decay, freq, k_scale, state, out, H, D, Dv, rot, P, CW, slices);
-    else if (tag == MIE_BF16)
-        return launch_kernel(retention_scan_kernel<bf16>, grid, dim3(threads), smem, stream, (const bf16*)qkv, (int64_t)stride,
-                             row_q_start, row_q_len, row_ctx_len, state_slots, decay, freq, k_scale, state, out, H, D, Dv, rot, P, CW, slices);
+    // chunks the step can have at most: every row one, and one more per RET_L tokens; those of rows with two or more
+    // (such a row has more than RET_L tokens): two per RET_L tokens
+    const int chunks1 = num_rows + num_tokens / RET_L, chunks0 = max_q_len > RET_L ? 2 * (num_tokens / RET_L) : 0;
+    if (chunks0 > scratch_chunks) return MIE_ERR_BAD_ARG;
+    const int prep_threads = H * D >= 1024 ? 256 : 128;
+    int rc;
+#define RET_LAUNCH(T)                                                                                                         \
+    rc = launch_kernel(retention_prepare_kernel<T>, dim3(num_tokens), dim3(prep_threads), (size_t)rot * sizeof(float), stream, \
+                       (const T*)qkv, (int64_t)stride, positions, freq, k_scale, qr, kr, H, D, rot);                          \
+    if (rc) return rc;                                                                                                        \
+    if (chunks0 > 0) {                                                                                                        \
+        rc = launch_kernel(retention_chunk_kernel<T, 0>, dim3(H * slices, chunks0), dim3(threads), smem, stream, qr, kr,      \
+                           (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state,     \
+                           scratch, out, num_rows, H, D, Dv, P, CW, slices);                                                  \
+        if (rc) return rc;                                                                                                    \
+        rc = launch_kernel(retention_combine_kernel, dim3(64, chunks0), dim3(256), 0, stream, row_q_len, state_slots, decay,  \
+                           (const float*)state, scratch, num_rows, H, Dv, D);                                                 \
+        if (rc) return rc;                                                                                                    \
+    }                                                                                                                         \
+    return launch_kernel(retention_chunk_kernel<T, 1>, dim3(H * slices, chunks1), dim3(threads), smem, stream, qr, kr,        \
+                         (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state,       \
+                         scratch, out, num_rows, H, D, Dv, P, CW, slices);
+    if (tag == MIE_F32) { RET_LAUNCH(float) }
+    else if (tag == MIE_BF16) { RET_LAUNCH(bf16) }
+#undef RET_LAUNCH
     return MIE_ERR_BAD_ARG;
 }
+
+extern "C" int mie_retention_chunk_tokens() { return RET_L; }
 
 extern "C" int mie_head_rms_gate(const float* o, const void* g, int tag, long long g_stride, void* out, int num_tokens, int H,
                                  int Dv, float eps, cudaStream_t stream) {

@@ -104,6 +104,14 @@ def linear_into_stream(x, w: torch.Tensor, bias, res: torch.Tensor, norm_weight,
 def linear(x, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
     M = x.shape[0]
     N = w.shape[0]
+    if (M and out_dtype == torch.float32 and not isinstance(x, gemm_tc.DeferredNorm) and x.dtype == torch.bfloat16 == w.dtype
+            and _bf16_backend != "simt" and x.is_cuda and not uses_tcgen05(x, w, out_dtype)):
+        # bfloat16 operands, float32 result (logits, what is added to a float32 stream) by the library: it would round
+        # its float32 accumulator to the output type, so ask for float32 directly; its result is the output
+        out = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if bias is not None:
+            out += bias
+        return out
     out = torch.empty(M, N, dtype=out_dtype, device=w.device)
     if M == 0:
         return out

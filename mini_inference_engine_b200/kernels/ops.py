@@ -623,11 +623,12 @@ def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out:
 
 # --------------------------------------------------------------------------- retention
 
-def retention_scan(qkv: torch.Tensor, row_q_start, row_q_len, row_ctx_len, state_slots, decay, freq, state, out, *,
-                   num_heads: int, dim: int, vdim: int, rot: int, k_scale: float) -> torch.Tensor:
+def retention_scan(qkv: torch.Tensor, positions, row_q_start, row_q_len, state_slots, decay, freq, state, out, *,
+                   num_heads: int, dim: int, vdim: int, rot: int, k_scale: float, max_q_len: int) -> torch.Tensor:
     """S <- decay_h S + k v^T, o = S^T q for every new token of every row, from and to ``state`` [slots, H, vdim, dim]
-    float32; q and k are rotated inside.  ``qkv`` rows hold [q: H x dim | k: H x dim | v: H x vdim | ...];
-    ``out`` [T, H * vdim] float32."""
+    float32; q and k are rotated (angle = position x ``freq``) and k scaled first.  ``qkv`` rows hold
+    [q: H x dim | k: H x dim | v: H x vdim | ...]; ``out`` [T, H * vdim] float32.  Rows longer than a chunk are cut
+    into chunks that run side by side (``max_q_len``: the longest row the launch may meet)."""
     T = qkv.shape[0]
     _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= num_heads * (2 * dim + vdim), "qkv rows must hold q, k and v")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (num_heads, vdim, dim),
@@ -635,12 +636,18 @@ def retention_scan(qkv: torch.Tensor, row_q_start, row_q_len, row_ctx_len, state
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, num_heads * vdim), "out must be float32 [T, H * vdim]")
     _need(decay.dtype == torch.float32 and decay.numel() == num_heads, "one float32 decay per head")
     _need(freq.dtype == torch.float32 and freq.numel() * 2 == rot, "one float32 frequency per rotated pair")
-    for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (row_ctx_len, "row_ctx_len"), (state_slots, "state_slots")):
+    for t, n in ((positions, "positions"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
         _i32(t, n)
+    _need(positions.numel() == T, "one position per token")
     lib = load("retention")
-    _check(lib.mie_retention_scan(_ptr(qkv), tag(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(row_q_start), _ptr(row_q_len),
-                                  _ptr(row_ctx_len), _ptr(state_slots), _ptr(decay), _ptr(freq), ctypes.c_float(k_scale),
-                                  _ptr(state), _ptr(out), row_q_len.numel(), num_heads, dim, vdim, rot, _stream()), "retention_scan")
+    chunk = lib.mie_retention_chunk_tokens()
+    chunks = 2 * (T // chunk) if max_q_len > chunk else 0
+    scratch = _workspace(qkv.device, "retention_chunks", chunks * num_heads * vdim * dim, torch.float32) if chunks else None
+    qr = torch.empty(2, T, num_heads * dim, dtype=torch.float32, device=qkv.device)
+    _check(lib.mie_retention_scan(_ptr(qkv), tag(qkv), ctypes.c_longlong(qkv.stride(0)), _ptr(positions), _ptr(row_q_start),
+                                  _ptr(row_q_len), _ptr(state_slots), _ptr(decay), _ptr(freq), ctypes.c_float(k_scale),
+                                  _ptr(state), _ptr(qr[0]), _ptr(qr[1]), _ptr(scratch), ctypes.c_longlong(chunks), _ptr(out), T,
+                                  row_q_len.numel(), int(max_q_len), num_heads, dim, vdim, rot, _stream()), "retention_scan")
     return out
 
 
@@ -661,35 +668,35 @@ def head_rms_gate(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_he
 
 def causal_conv(x: torch.Tensor, ctx_token_row, row_q_start, state_slots, taps, bias, state, u) -> torch.Tensor:
     """u[t] = bias + sum_j taps[:, j] x[t - (K-1) + j] per channel; inputs older than a row's portion come from rows
-    1.. of ``state`` [slots, K, C] float32.  ``x`` may be a column slice; ``u`` float32 [T, C]."""
+    1.. of ``state`` [slots, K, C] float32.  ``x`` may be a column slice; taps and bias float32; ``u`` float32 [T, C]."""
     T, C = x.shape
     K = taps.shape[1]
-    _need(x.stride(1) == 1 and taps.shape == (C, K) and taps.is_contiguous(), "conv taps must be [channels, taps]")
-    _need(bias is None or (bias.dtype == taps.dtype and bias.numel() == C), "conv bias must match the taps")
+    _need(x.stride(1) == 1 and taps.shape == (C, K) and taps.is_contiguous() and taps.dtype == torch.float32, "conv taps must be float32 [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == C), "conv bias must be float32, one per channel")
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (K, C), "state must be float32 [slots, K, C]")
     _need(u.dtype == torch.float32 and u.is_contiguous() and u.shape == (T, C), "u must be float32 [T, C]")
     for t, n in ((ctx_token_row, "token_row"), (row_q_start, "row_q_start"), (state_slots, "state_slots")):
         _i32(t, n)
     lib = load("linear_recurrence")
     _check(lib.mie_causal_conv(_ptr(x), tag(x), ctypes.c_longlong(x.stride(0)), _ptr(ctx_token_row), _ptr(row_q_start),
-                               _ptr(state_slots), _ptr(taps), _ptr(bias), tag(taps), _ptr(state), _ptr(u), T, C, K, _stream()),
+                               _ptr(state_slots), _ptr(taps), _ptr(bias), _ptr(state), _ptr(u), T, C, K, _stream()),
            "causal_conv")
     return u
 
 
 def recurrence_gates(u, w_a, b_a, w_i, b_i, lam, c_exp: float, a_out, b_out) -> None:
     """Block-diagonal gates and the recurrence's coefficients: a = exp(-c_exp * sigmoid(Wa u + ba) * softplus(lam)),
-    b = sqrt(1 - a^2) * sigmoid(Wi u + bi) * u, float32."""
+    b = sqrt(1 - a^2) * sigmoid(Wi u + bi) * u, all float32 (weights too)."""
     T, C = u.shape
     B, bw = w_a.shape[0], w_a.shape[1]
     _need(w_a.shape == (B, bw, bw) == w_i.shape and B * bw == C, "gate matrices must be [blocks, C / blocks, C / blocks]")
     ws = (w_a, b_a, w_i, b_i, lam)
-    _need(len({w.dtype for w in ws}) == 1 and all(w.is_contiguous() for w in ws), "gate weights must share a type")
+    _need(all(w.dtype == torch.float32 and w.is_contiguous() for w in ws), "gate weights must be contiguous float32")
     _need(b_a.numel() == C == b_i.numel() == lam.numel(), "gate biases and lam have one entry per channel")
     for t in (u, a_out, b_out):
         _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, C), "u, a and b must be float32 [T, C]")
     lib = load("linear_recurrence")
-    _check(lib.mie_recurrence_gates(_ptr(u), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(lam), tag(w_a), ctypes.c_float(c_exp),
+    _check(lib.mie_recurrence_gates(_ptr(u), _ptr(w_a), _ptr(b_a), _ptr(w_i), _ptr(b_i), _ptr(lam), ctypes.c_float(c_exp),
                                     _ptr(a_out), _ptr(b_out), T, C, B, _stream()), "recurrence_gates")
 
 

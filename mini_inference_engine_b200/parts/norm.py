@@ -60,7 +60,7 @@ class GroupRMSNorm(Part):
 
     def bind(self, tensors, rt):
         self.rt = rt
-        self.weight = rt.place(tensors["weight"])
+        self.weight = tensors["weight"].float().to(rt.device).contiguous()      # read as float32 by the kernel (16-byte loads)
 
     def kernel_sources(self):
         return {"norm_group"}

@@ -32,7 +32,7 @@ class ParallelMixers(Mixer):
         self.out_weights = []
         for name, b in zip(self.names, self.branches):
             b.bind({k: tensors[f"{name}.{k}"] for k in b.tensor_specs()}, rt)
-            self.out_weights.append(rt.place(tensors[f"{name}.out"]))
+            self.out_weights.append(tensors[f"{name}.out"].float().to(rt.device).contiguous())   # float32 for the norm kernel
 
     def cache_need(self):
         return tuple(b.cache_need() for b in self.branches)

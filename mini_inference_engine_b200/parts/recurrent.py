@@ -19,8 +19,8 @@ class GatedLinearRecurrence(Mixer):
     def __init__(self, hidden_size: int, width: int, blocks: int, taps: int, gate_constant: float = 8.0):
         if width % blocks:
             raise ValueError(f"{blocks} blocks do not divide {width} channels")
-        if not 1 <= taps <= 16:
-            raise ValueError(f"{taps} taps: the convolution kernel takes 1 to 16")
+        if not 1 <= taps <= 8:
+            raise ValueError(f"{taps} taps: the convolution kernel takes 1 to 8")
         self.hidden_size, self.width, self.blocks, self.taps, self.gate_constant = hidden_size, width, blocks, taps, gate_constant
 
     def tensor_specs(self):

@@ -5,7 +5,8 @@ a float32 state per request and head,
 
 with q and k rotated by position (k scaled by dim^-1/2 afterwards).  Each head's o is divided by its root mean
 square, the heads are multiplied by silu(W_g h) and projected by W_o.  The four projections of the input are one
-product; rotation, recurrence and the state's update are one kernel, the heads' norm and gate another.  The state
+product; the rotation is one kernel, the recurrence with the state's update runs in chunks side by side, the
+heads' norm and gate are another kernel.  The state
 (``StateNeed``) lives in the cache manager's state slots, so prompt portions and decoded tokens continue it alike."""
 from __future__ import annotations
 
@@ -53,8 +54,9 @@ class Retention(Mixer):
         H, D, Dv = self.num_heads, self.dim, self.vdim
         qkvg = self.rt.linear(x, self.w_qkvg)
         o = self.rt.empty(ctx.num_tokens, H * Dv, dtype=torch.float32)
-        ops.retention_scan(qkvg, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx_len, ctx.state_slots, self.decay_t, self.freq,
-                           cache.state, o, num_heads=H, dim=D, vdim=Dv, rot=self.rot_dims, k_scale=D ** -0.5)
+        ops.retention_scan(qkvg, ctx.positions, ctx.row_q_start, ctx.row_q_len, ctx.state_slots, self.decay_t, self.freq,
+                           cache.state, o, num_heads=H, dim=D, vdim=Dv, rot=self.rot_dims, k_scale=D ** -0.5,
+                           max_q_len=ctx.max_q_len)
         gated = self.rt.empty(ctx.num_tokens, H * Dv)
         ops.head_rms_gate(o, qkvg[:, 2 * H * D + H * Dv:], gated, H, Dv, self.eps)
         return self.rt.linear(gated, self.w_o, None, out_dtype=torch.float32)
