@@ -96,17 +96,18 @@ __device__ __forceinline__ int find_chunk(const int* __restrict__ row_q_len, int
     return -1;
 }
 
-template <typename T, int PASS>
+template <typename T, int PASS, int P>
 __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v,
                                        int64_t v_stride, const int* __restrict__ row_q_start,
                                        const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
                                        const float* __restrict__ decay, float* __restrict__ state,
                                        float* __restrict__ scratch, float* __restrict__ out, int num_rows, int H, int D, int Dv,
-                                       int P, int CW, int slices) {
+                                       int CW, int slices) {
+    constexpr int DPAD = P * RET_DPT;        // key dimensions as the threads of a column hold them: D padded with zeros
     extern __shared__ float smem[];
-    float* q_s = smem;                       // [RET_TT][D]
-    float* k_s = q_s + RET_TT * D;           // [RET_TT][D]
-    float* v_s = k_s + RET_TT * D;           // [RET_TT][CW]
+    float* q_s = smem;                       // [RET_TT][DPAD]
+    float* k_s = q_s + RET_TT * DPAD;        // [RET_TT][DPAD]
+    float* v_s = k_s + RET_TT * DPAD;        // [RET_TT][CW]
     pdl_enter();
     int within, items, before0;
     const int r = find_chunk(row_q_len, num_rows, (int)blockIdx.y, PASS, within, items, before0);
@@ -131,14 +132,17 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
             S[j] = (from && col_ok && d < D) ? from[d] : 0.f;
         }
     }
+    const float* k_mine = k_s + p;                                  // entry j of token tt: k_mine[tt * DPAD + P * j], offsets known at compile time
+    const float* q_mine = q_s + p;
+    const float* v_mine = v_s + (cl < CW ? cl : 0);
     for (int t0 = t_lo; t0 < t_hi; t0 += RET_TT) {
         const int nt = min(RET_TT, t_hi - t0);
         __syncthreads();
         const int64_t row0 = ((int64_t)(q_start + t0) * H + h) * D;
-        for (int i = threadIdx.x; i < nt * D; i += blockDim.x) {
-            const int tt = i / D, d = i - tt * D;
-            k_s[i] = kr[row0 + (int64_t)tt * H * D + d];
-            if (PASS) q_s[i] = qr[row0 + (int64_t)tt * H * D + d];
+        for (int i = threadIdx.x; i < nt * DPAD; i += blockDim.x) {
+            const int tt = i / DPAD, d = i % DPAD;
+            k_s[i] = d < D ? kr[row0 + (int64_t)tt * H * D + d] : 0.f;
+            if (PASS) q_s[i] = d < D ? qr[row0 + (int64_t)tt * H * D + d] : 0.f;
         }
         for (int i = threadIdx.x; i < nt * CW; i += blockDim.x) {
             const int tt = i / CW, cc = i - tt * CW;
@@ -146,20 +150,26 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
             v_s[i] = col < Dv ? to_f32<T>(v[(int64_t)(q_start + t0 + tt) * v_stride + h * Dv + col]) : 0.f;
         }
         __syncthreads();
+        float* o_ptr = out + (int64_t)(q_start + t0) * H * Dv + h * Dv + c;
         for (int tt = 0; tt < nt; ++tt) {
-            const float vv = cl < CW ? v_s[tt * CW + cl] : 0.f;
-            float acc = 0.f;
+            const float vv = v_mine[tt * CW];
+            const float* kt = k_mine + tt * DPAD;
+            const float* qt = q_mine + tt * DPAD;
+            float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < RET_DPT; ++j) {
-                const int d = p + P * j;
-                if (d < D) {
-                    S[j] = fmaf(gamma, S[j], k_s[tt * D + d] * vv);
-                    if (PASS) acc = fmaf(S[j], q_s[tt * D + d], acc);
+            for (int j = 0; j < RET_DPT; j += 2) {                  // padded dimensions hold zeros and stay zero
+                S[j] = fmaf(gamma, S[j], kt[P * j] * vv);
+                S[j + 1] = fmaf(gamma, S[j + 1], kt[P * (j + 1)] * vv);
+                if (PASS) {
+                    acc0 = fmaf(S[j], qt[P * j], acc0);
+                    acc1 = fmaf(S[j + 1], qt[P * (j + 1)], acc1);
                 }
             }
             if (PASS) {
+                float acc = acc0 + acc1;
+#pragma unroll
                 for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (p == 0 && col_ok) out[(int64_t)(q_start + t0 + tt) * H * Dv + h * Dv + c] = acc;
+                if (p == 0 && col_ok) o_ptr[(int64_t)tt * H * Dv] = acc;
             }
         }
     }
@@ -173,25 +183,37 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
     }
 }
 
-// scratch[j] becomes the state at the start of chunk j, for every row with two chunks or more
+// scratch[j] becomes the state at the start of chunk j, for every row with two chunks or more.  One thread per state
+// entry; every thread walks the rows (their lengths are the same few cached words for all) and, for a long row, the
+// row's chunks in order, eight loads ahead of the dependent multiply-adds.
 __global__ void retention_combine_kernel(const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
                                          const float* __restrict__ decay, const float* __restrict__ state,
                                          float* __restrict__ scratch, int num_rows, int H, int Dv, int D) {
     pdl_enter();
-    int within, items, before0;
-    const int r = find_chunk(row_q_len, num_rows, (int)blockIdx.y, 0, within, items, before0);
-    if (r < 0 || within != 0) return;                       // the block of a row's first chunk walks the whole row
     const int64_t per_state = (int64_t)H * Dv * D;
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < per_state; e += (int64_t)gridDim.x * blockDim.x) {
-        const int h = (int)(e / ((int64_t)Dv * D));
-        const float g = exp2f((float)RET_L * log2f(decay[h]));
+    const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per_state) return;
+    const int h = (int)(e / ((int64_t)Dv * D));
+    const float g = exp2f((float)RET_L * log2f(decay[h]));
+    int before0 = 0;
+    for (int r = 0; r < num_rows; ++r) {
+        const int items = (row_q_len[r] + RET_L - 1) / RET_L;
+        if (items < 2) continue;
         float cur = state[(int64_t)state_slots[r] * per_state + e];
-        scratch[(int64_t)before0 * per_state + e] = cur;
-        for (int j = 1; j < items; ++j) {
-            float* slot = scratch + (int64_t)(before0 + j) * per_state + e;
-            cur = fmaf(g, cur, *slot);
-            *slot = cur;
+        float* slot = scratch + (int64_t)before0 * per_state + e;
+        slot[0] = cur;
+        for (int j0 = 1; j0 < items; j0 += 8) {
+            float add[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) add[k] = j0 + k < items ? slot[(int64_t)(j0 + k) * per_state] : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (j0 + k < items) {
+                    cur = fmaf(g, cur, add[k]);
+                    slot[(int64_t)(j0 + k) * per_state] = cur;
+                }
         }
+        before0 += items;
     }
 }
 
@@ -230,32 +252,37 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
     if (CW > Dv) CW = Dv;
     const int slices = (Dv + CW - 1) / CW;
     const int threads = (CW * P + 31) / 32 * 32;
-    const size_t smem = (size_t)RET_TT * (2 * D + CW) * sizeof(float);
+    const size_t smem = (size_t)RET_TT * (2 * P * RET_DPT + CW) * sizeof(float);
     // chunks the step can have at most: every row one, and one more per RET_L tokens; those of rows with two or more
     // (such a row has more than RET_L tokens): two per RET_L tokens
     const int chunks1 = num_rows + num_tokens / RET_L, chunks0 = max_q_len > RET_L ? 2 * (num_tokens / RET_L) : 0;
     if (chunks0 > scratch_chunks) return MIE_ERR_BAD_ARG;
     const int prep_threads = H * D >= 1024 ? 256 : 128;
     int rc;
+#define RET_PASS(T, PASS, PP, ny)                                                                                             \
+    launch_kernel(retention_chunk_kernel<T, PASS, PP>, dim3(H * slices, ny), dim3(threads), smem, stream, qr, kr,             \
+                  (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state, scratch,     \
+                  out, num_rows, H, D, Dv, CW, slices)
+#define RET_PASS_P(T, PASS, ny)                                                                                               \
+    (P == 1 ? RET_PASS(T, PASS, 1, ny) : P == 2 ? RET_PASS(T, PASS, 2, ny) : P == 4 ? RET_PASS(T, PASS, 4, ny)                \
+     : P == 8 ? RET_PASS(T, PASS, 8, ny) : P == 16 ? RET_PASS(T, PASS, 16, ny) : RET_PASS(T, PASS, 32, ny))
 #define RET_LAUNCH(T)                                                                                                         \
     rc = launch_kernel(retention_prepare_kernel<T>, dim3(num_tokens), dim3(prep_threads), (size_t)rot * sizeof(float), stream, \
                        (const T*)qkv, (int64_t)stride, positions, freq, k_scale, qr, kr, H, D, rot);                          \
     if (rc) return rc;                                                                                                        \
     if (chunks0 > 0) {                                                                                                        \
-        rc = launch_kernel(retention_chunk_kernel<T, 0>, dim3(H * slices, chunks0), dim3(threads), smem, stream, qr, kr,      \
-                           (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state,     \
-                           scratch, out, num_rows, H, D, Dv, P, CW, slices);                                                  \
+        rc = RET_PASS_P(T, 0, chunks0);                                                                                       \
         if (rc) return rc;                                                                                                    \
-        rc = launch_kernel(retention_combine_kernel, dim3(64, chunks0), dim3(256), 0, stream, row_q_len, state_slots, decay,  \
-                           (const float*)state, scratch, num_rows, H, Dv, D);                                                 \
+        rc = launch_kernel(retention_combine_kernel, dim3((unsigned)(((int64_t)H * Dv * D + 255) / 256)), dim3(256), 0, stream, \
+                           row_q_len, state_slots, decay, (const float*)state, scratch, num_rows, H, Dv, D);                  \
         if (rc) return rc;                                                                                                    \
     }                                                                                                                         \
-    return launch_kernel(retention_chunk_kernel<T, 1>, dim3(H * slices, chunks1), dim3(threads), smem, stream, qr, kr,        \
-                         (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state,       \
-                         scratch, out, num_rows, H, D, Dv, P, CW, slices);
+    return RET_PASS_P(T, 1, chunks1);
     if (tag == MIE_F32) { RET_LAUNCH(float) }
     else if (tag == MIE_BF16) { RET_LAUNCH(bf16) }
 #undef RET_LAUNCH
+#undef RET_PASS_P
+#undef RET_PASS
     return MIE_ERR_BAD_ARG;
 }
 
