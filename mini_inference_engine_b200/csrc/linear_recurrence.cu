@@ -52,29 +52,28 @@ __global__ void causal_conv_kernel(const T* __restrict__ x, int64_t x_stride, co
     }
 }
 
-// A tile of GATE_TM tokens x 16 JN output channels of one channel block per thread block (16 x 16 threads, 4 tokens x
+// A tile of 64 IM tokens x 16 JN output channels of one channel block per thread block (16 x 16 threads, 4 IM tokens x
 // JN outputs of both gate matrices a thread); u and both weight tiles go through shared memory GATE_TK input
 // channels at a time, transposed so that a thread reads its four tokens (and, with JN = 4, its four channels) as one
 // float4.  JN = 4 for prompt portions; JN = 1 for steps of few tokens, which then have four times as many blocks to
 // stream the weights with.
-#define GATE_TM 64
 #define GATE_TK 16
-template <int JN>
+template <int JN, int IM>                 // JN outputs and 4 IM tokens a thread: a tile of 64 IM tokens x 16 JN outputs
 __global__ void __launch_bounds__(256) recurrence_gates_kernel(
         const float* __restrict__ u, const float* __restrict__ wa, const float* __restrict__ ba, const float* __restrict__ wi,
         const float* __restrict__ bi, const float* __restrict__ lam, float c_exp, float* __restrict__ a_out,
         float* __restrict__ b_out, int num_tokens, int C, int bw, int n_tiles) {
-    constexpr int TN = 16 * JN;
+    constexpr int TN = 16 * JN, GATE_TM = 64 * IM;
     __shared__ __align__(16) float u_s[GATE_TK][GATE_TM + 4];
     __shared__ __align__(16) float wa_s[GATE_TK][TN + 4];
     __shared__ __align__(16) float wi_s[GATE_TK][TN + 4];
     pdl_enter();
     const int blk = blockIdx.y / n_tiles, o0 = (blockIdx.y - blk * n_tiles) * TN;
     const int t0 = blockIdx.x * GATE_TM;
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // tx: outputs JN tx .. JN tx + JN - 1, ty: tokens 4 ty .. 4 ty + 3
-    float ra[4][JN], ri[4][JN];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // tx: outputs JN tx .. JN tx + JN - 1, ty: tokens 4 IM ty .. 4 IM ty + 4 IM - 1
+    float ra[4 * IM][JN], ri[4 * IM][JN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4 * IM; ++i)
 #pragma unroll
         for (int j = 0; j < JN; ++j) { ra[i][j] = 0.f; ri[i][j] = 0.f; }
     for (int k0 = 0; k0 < bw; k0 += GATE_TK) {
@@ -93,13 +92,17 @@ __global__ void __launch_bounds__(256) recurrence_gates_kernel(
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < GATE_TK; ++kk) {
-            const float4 uv = *reinterpret_cast<const float4*>(&u_s[kk][4 * ty]);
-            const float uu[4] = {uv.x, uv.y, uv.z, uv.w};
+            float uu[4 * IM];
+#pragma unroll
+            for (int m = 0; m < IM; ++m) {
+                const float4 uv = *reinterpret_cast<const float4*>(&u_s[kk][4 * IM * ty + 4 * m]);
+                uu[4 * m] = uv.x; uu[4 * m + 1] = uv.y; uu[4 * m + 2] = uv.z; uu[4 * m + 3] = uv.w;
+            }
             float aa[JN], ii[JN];
 #pragma unroll
             for (int j = 0; j < JN; ++j) { aa[j] = wa_s[kk][JN * tx + j]; ii[j] = wi_s[kk][JN * tx + j]; }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 4 * IM; ++i)
 #pragma unroll
                 for (int j = 0; j < JN; ++j) {
                     ra[i][j] = fmaf(uu[i], aa[j], ra[i][j]);
@@ -115,8 +118,8 @@ __global__ void __launch_bounds__(256) recurrence_gates_kernel(
         const float bra = ba[ch], bri = bi[ch], l = lam[ch];
         const float sp = l > 20.f ? l : log1pf(expf(l));                  // softplus
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int t = t0 + 4 * ty + i;
+        for (int i = 0; i < 4 * IM; ++i) {
+            const int t = t0 + 4 * IM * ty + i;
             if (t >= num_tokens) continue;
             const float r = 1.0f / (1.0f + expf(-(ra[i][j] + bra)));
             const float g = 1.0f / (1.0f + expf(-(ri[i][j] + bri)));
@@ -214,14 +217,16 @@ extern "C" int mie_recurrence_gates(const float* u, const float* wa, const float
     if (num_tokens <= 0) return 0;
     if (C <= 0 || blocks <= 0 || C % blocks) return MIE_ERR_BAD_ARG;
     const int bw = C / blocks;
-    const int token_tiles = (num_tokens + GATE_TM - 1) / GATE_TM;
+    const int token_tiles = (num_tokens + 63) / 64;
     if (token_tiles * ((bw + 63) / 64) * blocks >= 2 * device_sm_count()) {
+        // 4 tokens x 4 outputs a thread; 8 x 4 (IM = 2) takes 107 registers and was measured slower: 229 against 183 us
+        // at 2,048 tokens, 8 blocks of 256 channels
         const int n_tiles = (bw + 63) / 64;
-        return launch_kernel(recurrence_gates_kernel<4>, dim3(token_tiles, blocks * n_tiles), dim3(256), 0, stream, u, wa, ba, wi, bi,
+        return launch_kernel(recurrence_gates_kernel<4, 1>, dim3(token_tiles, blocks * n_tiles), dim3(256), 0, stream, u, wa, ba, wi, bi,
                              lam, c_exp, a_out, b_out, num_tokens, C, bw, n_tiles);
     }
     const int n_tiles = (bw + 15) / 16;
-    return launch_kernel(recurrence_gates_kernel<1>, dim3(token_tiles, blocks * n_tiles), dim3(256), 0, stream, u, wa, ba, wi, bi,
+    return launch_kernel(recurrence_gates_kernel<1, 1>, dim3(token_tiles, blocks * n_tiles), dim3(256), 0, stream, u, wa, ba, wi, bi,
                          lam, c_exp, a_out, b_out, num_tokens, C, bw, n_tiles);
 }
 

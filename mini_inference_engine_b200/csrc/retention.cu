@@ -20,8 +20,8 @@
 // lengths on the device, so the launch is laid out for the step's token count, not for what the host knows of its rows.
 //
 // Work split of a pass: one block = one chunk, one head and a slice of value columns.  A column's state is held in
-// the registers of P threads of one warp (thread p holds the key dimensions p, p + P, p + 2P, ...: up to RET_DPT of
-// them), which add up their parts of o_t by shuffles.  Tokens are staged in shared memory RET_TT at a time.
+// the registers of P threads of one warp (thread p holds the key dimensions 4 (p + P j) .. 4 (p + P j) + 3, j = 0 ..:
+// RET_DPT of them, read from shared memory as float4), which add up their parts of o_t by shuffles.  Tokens are staged in shared memory RET_TT at a time.
 // Everything is float32.
 //
 // The last kernel finishes the mixer's head stage: every head's o is divided by its root mean square (no
@@ -128,12 +128,14 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
         const float* from = PASS == 0 ? nullptr : (items == 1 ? st : scratch + (int64_t)(before0 + within) * per_state + hcol);
 #pragma unroll
         for (int j = 0; j < RET_DPT; ++j) {
-            const int d = p + P * j;
+            const int d = 4 * (p + P * (j >> 2)) + (j & 3);
             S[j] = (from && col_ok && d < D) ? from[d] : 0.f;
         }
     }
-    const float* k_mine = k_s + p;                                  // entry j of token tt: k_mine[tt * DPAD + P * j], offsets known at compile time
-    const float* q_mine = q_s + p;
+    // S[4 j4 + e] is key dimension 4 (p + P j4) + e: a thread reads its dimensions of a token as RET_DPT / 4 float4,
+    // the P threads of a column 16 P contiguous bytes at a time, at offsets known at compile time
+    const float4* k_mine = reinterpret_cast<const float4*>(k_s) + p;
+    const float4* q_mine = reinterpret_cast<const float4*>(q_s) + p;
     const float* v_mine = v_s + (cl < CW ? cl : 0);
     for (int t0 = t_lo; t0 < t_hi; t0 += RET_TT) {
         const int nt = min(RET_TT, t_hi - t0);
@@ -153,16 +155,22 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
         float* o_ptr = out + (int64_t)(q_start + t0) * H * Dv + h * Dv + c;
         for (int tt = 0; tt < nt; ++tt) {
             const float vv = v_mine[tt * CW];
-            const float* kt = k_mine + tt * DPAD;
-            const float* qt = q_mine + tt * DPAD;
+            const float4* kt = k_mine + tt * (DPAD / 4);
+            const float4* qt = q_mine + tt * (DPAD / 4);
             float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < RET_DPT; j += 2) {                  // padded dimensions hold zeros and stay zero
-                S[j] = fmaf(gamma, S[j], kt[P * j] * vv);
-                S[j + 1] = fmaf(gamma, S[j + 1], kt[P * (j + 1)] * vv);
+            for (int j4 = 0; j4 < RET_DPT / 4; ++j4) {              // padded dimensions hold zeros and stay zero
+                const float4 kk = kt[P * j4];
+                S[4 * j4 + 0] = fmaf(gamma, S[4 * j4 + 0], kk.x * vv);
+                S[4 * j4 + 1] = fmaf(gamma, S[4 * j4 + 1], kk.y * vv);
+                S[4 * j4 + 2] = fmaf(gamma, S[4 * j4 + 2], kk.z * vv);
+                S[4 * j4 + 3] = fmaf(gamma, S[4 * j4 + 3], kk.w * vv);
                 if (PASS) {
-                    acc0 = fmaf(S[j], qt[P * j], acc0);
-                    acc1 = fmaf(S[j + 1], qt[P * (j + 1)], acc1);
+                    const float4 qq = qt[P * j4];
+                    acc0 = fmaf(S[4 * j4 + 0], qq.x, acc0);
+                    acc1 = fmaf(S[4 * j4 + 1], qq.y, acc1);
+                    acc0 = fmaf(S[4 * j4 + 2], qq.z, acc0);
+                    acc1 = fmaf(S[4 * j4 + 3], qq.w, acc1);
                 }
             }
             if (PASS) {
@@ -177,7 +185,7 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
     if (to && col_ok) {
 #pragma unroll
         for (int j = 0; j < RET_DPT; ++j) {
-            const int d = p + P * j;
+            const int d = 4 * (p + P * (j >> 2)) + (j & 3);
             if (d < D) to[d] = S[j];
         }
     }
