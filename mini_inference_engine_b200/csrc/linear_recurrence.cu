@@ -137,7 +137,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 
 // blockDim = (channels, segments)
 template <typename T>
-__global__ void recurrence_scan_kernel(const float* __restrict__ a, const float* __restrict__ b, const T* __restrict__ y,
+__global__ void __launch_bounds__(1024) recurrence_scan_kernel(const float* __restrict__ a, const float* __restrict__ b, const T* __restrict__ y,
                                        int64_t y_stride, const T* __restrict__ x, int64_t x_stride,
                                        const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
                                        const int* __restrict__ state_slots, float* __restrict__ state, T* __restrict__ out,
@@ -159,12 +159,19 @@ __global__ void recurrence_scan_kernel(const float* __restrict__ a, const float*
     if (nseg > 1) {
         float A = 1.f, Bv = 0.f;
         if (ok)
-#pragma unroll 8
-            for (int t = lo; t < hi; ++t) {
-                const int64_t i = (int64_t)(q_start + t) * C + ch;
-                const float at = a[i];
-                A *= at;
-                Bv = fmaf(at, Bv, b[i]);
+            for (int t = lo; t < hi; t += 8) {                // eight tokens' loads in flight before the dependent chain
+                float av[8], bv[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int64_t i = (int64_t)(q_start + t + k) * C + ch;
+                    av[k] = t + k < hi ? a[i] : 1.f;
+                    bv[k] = t + k < hi ? b[i] : 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    A *= av[k];
+                    Bv = fmaf(av[k], Bv, bv[k]);
+                }
             }
         A_s[seg * nch + threadIdx.x] = A;
         B_s[seg * nch + threadIdx.x] = Bv;
@@ -172,11 +179,21 @@ __global__ void recurrence_scan_kernel(const float* __restrict__ a, const float*
     }
     if (!ok) return;
     for (int k = 0; k < seg; ++k) s = fmaf(A_s[k * nch + threadIdx.x], s, B_s[k * nch + threadIdx.x]);
-#pragma unroll 8
-    for (int t = lo; t < hi; ++t) {
-        const int64_t i = (int64_t)(q_start + t) * C + ch;
-        s = fmaf(a[i], s, b[i]);
-        out[i] = from_f32<T>(s * gelu_tanh_f(to_f32<T>(y[(int64_t)(q_start + t) * y_stride + ch])));
+    for (int t = lo; t < hi; t += 8) {
+        float av[8], bv[8], yv[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool in = t + k < hi;
+            const int64_t i = (int64_t)(q_start + t + k) * C + ch;
+            av[k] = in ? a[i] : 1.f;
+            bv[k] = in ? b[i] : 0.f;
+            yv[k] = in ? to_f32<T>(y[(int64_t)(q_start + t + k) * y_stride + ch]) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            s = fmaf(av[k], s, bv[k]);                          // past the end: a = 1, b = 0 leave s as it is
+            if (t + k < hi) out[(int64_t)(q_start + t + k) * C + ch] = from_f32<T>(s * gelu_tanh_f(yv[k]));
+        }
     }
     if (hi == q_len && lo < q_len) st[ch] = s;                // the segment that holds the last token
     if (seg == 0) {

@@ -64,14 +64,10 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int64_t qkv_strid
         return d < half ? own * c - other * sn : own * c + other * sn;
     };
     T* qo = q_out + (int64_t)t * H * DP;
-    for (int i = threadIdx.x; i < H * DP; i += blockDim.x) {
-        const int h = i / DP, d = i - h * DP;
-        float val = 0.f;
-        if (d < D) {
-            val = entry(q, qw, sq, h, d) * q_scale;
-            if (temp) val *= load_tagged(temp, h, w_tag);
-        }
-        qo[i] = from_f32<T>(val);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int h = warp; h < H; h += nw) {                      // a head a warp, a dimension a lane: no divisions
+        const float hs = temp ? q_scale * load_tagged(temp, h, w_tag) : q_scale;
+        for (int d = lane; d < DP; d += 32) qo[h * DP + d] = from_f32<T>(d < D ? entry(q, qw, sq, h, d) * hs : 0.f);
     }
     if (!write_cache) return;
     const int slot = slots[t];
@@ -80,11 +76,12 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ qkv, int64_t qkv_strid
         return;
     }
     const int page = slot / page_size, off = slot - page * page_size;
-    for (int i = threadIdx.x; i < G * DP; i += blockDim.x) {
-        const int g = i / DP, d = i - g * DP;
-        const int64_t dst = (((int64_t)page * G + g) * page_size + off) * DP + d;
-        k_cache[dst] = from_f32<T>(d < D ? entry(k, kw, sk, g, d) * k_scale : 0.f);
-        v_cache[dst] = d < Dv ? v[g * Dv + d] : from_f32<T>(0.f);
+    for (int g = warp; g < G; g += nw) {
+        const int64_t row = (((int64_t)page * G + g) * page_size + off) * DP;
+        for (int d = lane; d < DP; d += 32) {
+            k_cache[row + d] = from_f32<T>(d < D ? entry(k, kw, sk, g, d) * k_scale : 0.f);
+            v_cache[row + d] = d < Dv ? v[g * Dv + d] : from_f32<T>(0.f);
+        }
     }
 }
 
