@@ -114,12 +114,18 @@ class DecoderModel:
         return self.storage
 
     def weight_bytes(self) -> int:
+        from ..parts.base import Part
         seen, total = set(), 0
-        for obj in [self.embedding, self.final_norm, self.head] + [p for b in self.blocks for p in b.parts()]:
+        todo = [self.embedding, self.final_norm, self.head] + [p for b in self.blocks for p in b.parts()]
+        while todo:                                   # parts may hold parts (mixers side by side, an embedding's norm)
+            obj = todo.pop()
             for v in vars(obj).values():
-                if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
-                    seen.add(v.data_ptr())
-                    total += v.numel() * v.element_size()
+                for item in (v if isinstance(v, (list, tuple)) else (v,)):
+                    if isinstance(item, torch.Tensor) and item.data_ptr() not in seen:
+                        seen.add(item.data_ptr())
+                        total += item.numel() * item.element_size()
+                    elif isinstance(item, Part):
+                        todo.append(item)
         return total
 
     # ------------------------------------------------------------------ the step function
