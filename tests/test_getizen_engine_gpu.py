@@ -54,8 +54,13 @@ CONFIGS = {
         with_mlp(retention(1, 64, 64, [0.98], 64, base=500.0), 96, 2.0),
         with_mlp(parallel(1, 1, 64, 64, 64, 64, 64, 4, 1), 96, 2.0),
         with_mlp(parallel(4, 1, 64, 48, 16, 32, 32, 2, 6), None, 0)]),
+    # heads of 128 (in bfloat16: page copies by TMA in decoding, the tcgen05 kernel for portions), retention with eight
+    # threads a value column, a recurrence wider than the model, five norm groups
+    "g_c": dict(architecture="Getizen", vocab=211, width=80, postln_alpha=2.0, norm=dict(eps=1e-5, groups=5), layers=[
+        with_mlp(retention(2, 128, 64, [0.97, 0.999], 64), 48, 4.0),
+        with_mlp(parallel(2, 1, 128, 128, 48, 128, 96, 3, 4, scaling=dict(factor=2.0, low=1.0, high=2.0, original=64), base=1e3), 112, 1.0)]),
 }
-LENGTHS = {"g_a": [5, 77, 130, 2, 49, 24, 25], "g_b": [1, 70, 33, 129, 16, 17, 64]}
+LENGTHS = {"g_a": [5, 77, 130, 2, 49, 24, 25], "g_b": [1, 70, 33, 129, 16, 17, 64], "g_c": [3, 100, 47, 150, 48, 49, 9]}
 
 
 @pytest.fixture(scope="module")
