@@ -19,7 +19,7 @@
 // A step whose rows all fit one chunk (decoding) runs pass 1 only.  Blocks find their (row, chunk) from the rows'
 // lengths on the device, so the launch is laid out for the step's token count, not for what the host knows of its rows.
 //
-// Work split of a pass: one block = one chunk, one head and a slice of value columns.  A column's state is held in
+// Work split of a pass: one block = one chunk, one head and a slice of value columns (one or two a thread).  A column's state is held in
 // the registers of P threads of one warp (thread p holds the key dimensions 4 (p + P j) .. 4 (p + P j) + 3, j = 0 ..:
 // RET_DPT of them, read from shared memory as float4), which add up their parts of o_t by shuffles.  Tokens are staged in shared memory RET_TT at a time.
 // Everything is float32.
@@ -96,7 +96,7 @@ __device__ __forceinline__ int find_chunk(const int* __restrict__ row_q_len, int
     return -1;
 }
 
-template <typename T, int PASS, int P>
+template <typename T, int PASS, int P, int NC>
 __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float* __restrict__ kr, const T* __restrict__ v,
                                        int64_t v_stride, const int* __restrict__ row_q_start,
                                        const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
@@ -115,28 +115,33 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
     const int h = blockIdx.x / slices, slice = blockIdx.x - h * slices;
     const int q_len = row_q_len[r], q_start = row_q_start[r];
     const int t_lo = within * RET_L, t_hi = min(q_len, t_lo + RET_L);
-    const int p = threadIdx.x % P, cl = threadIdx.x / P;
-    const int c = slice * CW + cl;                                  // this thread's value column
-    const bool col_ok = cl < CW && c < Dv;
+    // a thread holds NC value columns, CW / NC apart (the key and query it reads from shared memory serve all of them)
+    const int p = threadIdx.x % P, cl = threadIdx.x / P, cstep = CW / NC;
     const float gamma = decay[h];
-    const int64_t hcol = ((int64_t)h * Dv + (col_ok ? c : 0)) * D;
     const int64_t per_state = (int64_t)H * Dv * D;
-    float* st = state + (int64_t)state_slots[r] * per_state + hcol;
-    float S[RET_DPT];
-    {
-        // pass 0 builds from zero; pass 1 starts from the request's state or from what the combine left for this chunk
-        const float* from = PASS == 0 ? nullptr : (items == 1 ? st : scratch + (int64_t)(before0 + within) * per_state + hcol);
+    int c[NC];
+    bool col_ok[NC];
+    int64_t hcol[NC];
+    float S[NC][RET_DPT];
+    // pass 0 builds from zero; pass 1 starts from the request's state or from what the combine left for this chunk
+    const float* from = PASS == 0 ? nullptr : (items == 1 ? state + (int64_t)state_slots[r] * per_state
+                                                           : scratch + (int64_t)(before0 + within) * per_state);
+#pragma unroll
+    for (int n = 0; n < NC; ++n) {
+        c[n] = slice * CW + cl + n * cstep;
+        col_ok[n] = cl < cstep && c[n] < Dv;
+        hcol[n] = ((int64_t)h * Dv + (col_ok[n] ? c[n] : 0)) * D;
 #pragma unroll
         for (int j = 0; j < RET_DPT; ++j) {
             const int d = 4 * (p + P * (j >> 2)) + (j & 3);
-            S[j] = (from && col_ok && d < D) ? from[d] : 0.f;
+            S[n][j] = (from && col_ok[n] && d < D) ? from[hcol[n] + d] : 0.f;
         }
     }
     // S[4 j4 + e] is key dimension 4 (p + P j4) + e: a thread reads its dimensions of a token as RET_DPT / 4 float4,
     // the P threads of a column 16 P contiguous bytes at a time, at offsets known at compile time
     const float4* k_mine = reinterpret_cast<const float4*>(k_s) + p;
     const float4* q_mine = reinterpret_cast<const float4*>(q_s) + p;
-    const float* v_mine = v_s + (cl < CW ? cl : 0);
+    const float* v_mine = v_s + (cl < cstep ? cl : 0);
     for (int t0 = t_lo; t0 < t_hi; t0 += RET_TT) {
         const int nt = min(RET_TT, t_hi - t0);
         __syncthreads();
@@ -152,41 +157,54 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
             v_s[i] = col < Dv ? to_f32<T>(v[(int64_t)(q_start + t0 + tt) * v_stride + h * Dv + col]) : 0.f;
         }
         __syncthreads();
-        float* o_ptr = out + (int64_t)(q_start + t0) * H * Dv + h * Dv + c;
+        float* o_ptr = out + (int64_t)(q_start + t0) * H * Dv + h * Dv;
         for (int tt = 0; tt < nt; ++tt) {
-            const float vv = v_mine[tt * CW];
+            float vv[NC], acc0[NC], acc1[NC];
+#pragma unroll
+            for (int n = 0; n < NC; ++n) { vv[n] = v_mine[tt * CW + n * cstep]; acc0[n] = 0.f; acc1[n] = 0.f; }
             const float4* kt = k_mine + tt * (DPAD / 4);
             const float4* qt = q_mine + tt * (DPAD / 4);
-            float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
             for (int j4 = 0; j4 < RET_DPT / 4; ++j4) {              // padded dimensions hold zeros and stay zero
                 const float4 kk = kt[P * j4];
-                S[4 * j4 + 0] = fmaf(gamma, S[4 * j4 + 0], kk.x * vv);
-                S[4 * j4 + 1] = fmaf(gamma, S[4 * j4 + 1], kk.y * vv);
-                S[4 * j4 + 2] = fmaf(gamma, S[4 * j4 + 2], kk.z * vv);
-                S[4 * j4 + 3] = fmaf(gamma, S[4 * j4 + 3], kk.w * vv);
-                if (PASS) {
-                    const float4 qq = qt[P * j4];
-                    acc0 = fmaf(S[4 * j4 + 0], qq.x, acc0);
-                    acc1 = fmaf(S[4 * j4 + 1], qq.y, acc1);
-                    acc0 = fmaf(S[4 * j4 + 2], qq.z, acc0);
-                    acc1 = fmaf(S[4 * j4 + 3], qq.w, acc1);
+                float4 qq = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (PASS) qq = qt[P * j4];
+#pragma unroll
+                for (int n = 0; n < NC; ++n) {
+                    S[n][4 * j4 + 0] = fmaf(gamma, S[n][4 * j4 + 0], kk.x * vv[n]);
+                    S[n][4 * j4 + 1] = fmaf(gamma, S[n][4 * j4 + 1], kk.y * vv[n]);
+                    S[n][4 * j4 + 2] = fmaf(gamma, S[n][4 * j4 + 2], kk.z * vv[n]);
+                    S[n][4 * j4 + 3] = fmaf(gamma, S[n][4 * j4 + 3], kk.w * vv[n]);
+                    if (PASS) {
+                        acc0[n] = fmaf(S[n][4 * j4 + 0], qq.x, acc0[n]);
+                        acc1[n] = fmaf(S[n][4 * j4 + 1], qq.y, acc1[n]);
+                        acc0[n] = fmaf(S[n][4 * j4 + 2], qq.z, acc0[n]);
+                        acc1[n] = fmaf(S[n][4 * j4 + 3], qq.w, acc1[n]);
+                    }
                 }
             }
             if (PASS) {
-                float acc = acc0 + acc1;
 #pragma unroll
-                for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (p == 0 && col_ok) o_ptr[(int64_t)tt * H * Dv] = acc;
+                for (int n = 0; n < NC; ++n) {
+                    float acc = acc0[n] + acc1[n];
+#pragma unroll
+                    for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (p == 0 && col_ok[n]) o_ptr[(int64_t)tt * H * Dv + c[n]] = acc;
+                }
             }
         }
     }
-    float* to = PASS == 0 ? scratch + (int64_t)(before0 + within + 1) * per_state + hcol : (within == items - 1 ? st : nullptr);
-    if (to && col_ok) {
+    float* to = PASS == 0 ? scratch + (int64_t)(before0 + within + 1) * per_state
+                          : (within == items - 1 ? state + (int64_t)state_slots[r] * per_state : nullptr);
+    if (to) {
 #pragma unroll
-        for (int j = 0; j < RET_DPT; ++j) {
-            const int d = 4 * (p + P * (j >> 2)) + (j & 3);
-            if (d < D) to[d] = S[j];
+        for (int n = 0; n < NC; ++n) {
+            if (!col_ok[n]) continue;
+#pragma unroll
+            for (int j = 0; j < RET_DPT; ++j) {
+                const int d = 4 * (p + P * (j >> 2)) + (j & 3);
+                if (d < D) to[hcol[n] + d] = S[n][j];
+            }
         }
     }
 }
@@ -256,11 +274,22 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
     int P = 1;
     while (P * RET_DPT < D) P <<= 1;
     if (P > 32) return MIE_ERR_TOO_LARGE;                      // key dimensions beyond 32 x RET_DPT
-    int CW = 256 / P;
-    if (CW > Dv) CW = Dv;
-    const int slices = (Dv + CW - 1) / CW;
-    const int threads = (CW * P + 31) / 32 * 32;
-    const size_t smem = (size_t)RET_TT * (2 * P * RET_DPT + CW) * sizeof(float);
+    // Value columns a thread.  Pass 0 (no outputs): two where the head has enough of them to fill 256 threads that way --
+    // its shared-memory reads of k then serve twice the multiply-adds (107 -> 90 us at 8 heads of 128 x 256, 2,048
+    // tokens).  Pass 1 stays with one: with two it takes 72 registers, three blocks an SM instead of six, and was
+    // measured slower (188 -> 231 us).  The state's layout does not depend on how a pass cuts the columns.
+    struct Cut { int NC, CW, slices, threads; size_t smem; };
+    auto cut = [&](int nc) {
+        Cut c;
+        c.NC = nc;
+        c.CW = nc * (256 / P);                                 // columns a block
+        if (c.CW > Dv) c.CW = Dv;
+        c.slices = (Dv + c.CW - 1) / c.CW;
+        c.threads = (c.CW / nc * P + 31) / 32 * 32;
+        c.smem = (size_t)RET_TT * (2 * P * RET_DPT + c.CW) * sizeof(float);
+        return c;
+    };
+    const Cut cut0 = cut(Dv >= 2 * (256 / P) ? 2 : 1), cut1 = cut(1);
     // chunks the step can have at most: every row one, and one more per RET_L tokens; those of rows with two or more
     // (such a row has more than RET_L tokens): two per RET_L tokens
     const int chunks1 = num_rows + num_tokens / RET_L, chunks0 = max_q_len > RET_L ? 2 * (num_tokens / RET_L) : 0;
@@ -268,9 +297,11 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
     const int prep_threads = H * D >= 1024 ? 256 : 128;
     int rc;
 #define RET_PASS(T, PASS, PP, ny)                                                                                             \
-    launch_kernel(retention_chunk_kernel<T, PASS, PP>, dim3(H * slices, ny), dim3(threads), smem, stream, qr, kr,             \
-                  (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state, scratch,     \
-                  out, num_rows, H, D, Dv, CW, slices)
+    ((PASS == 0 && cut0.NC == 2) ? RET_PASS_N(T, 0, PP, 2, ny, cut0) : RET_PASS_N(T, PASS, PP, 1, ny, (PASS == 0 ? cut0 : cut1)))
+#define RET_PASS_N(T, PASS, PP, NN, ny, CUT)                                                                                  \
+    launch_kernel(retention_chunk_kernel<T, PASS, PP, NN>, dim3(H * CUT.slices, ny), dim3(CUT.threads), CUT.smem, stream, qr, \
+                  kr, (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state, scratch, \
+                  out, num_rows, H, D, Dv, CUT.CW, CUT.slices)
 #define RET_PASS_P(T, PASS, ny)                                                                                               \
     (P == 1 ? RET_PASS(T, PASS, 1, ny) : P == 2 ? RET_PASS(T, PASS, 2, ny) : P == 4 ? RET_PASS(T, PASS, 4, ny)                \
      : P == 8 ? RET_PASS(T, PASS, 8, ny) : P == 16 ? RET_PASS(T, PASS, 16, ny) : RET_PASS(T, PASS, 32, ny))
@@ -291,6 +322,7 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
 #undef RET_LAUNCH
 #undef RET_PASS_P
 #undef RET_PASS
+#undef RET_PASS_N
     return MIE_ERR_BAD_ARG;
 }
 

@@ -142,7 +142,8 @@ def test_clamped_feed_forward(dt):
 
 RETENTIONS = [dict(num_heads=3, dim=16, vdim=32, decay=(0.5, 0.9, 0.999), rot_dims=8),          # key and value sizes differ, part of a head turns
               dict(num_heads=1, dim=48, vdim=16, decay=(0.97,), rot_dims=48),                    # one head, three threads a column
-              dict(num_heads=2, dim=80, vdim=40, decay=(1.0, 0.75), rot_dims=0)]                 # no decay at all, no rotation
+              dict(num_heads=2, dim=80, vdim=40, decay=(1.0, 0.75), rot_dims=0),                 # no decay at all, no rotation
+              dict(num_heads=1, dim=64, vdim=136, decay=(0.9,), rot_dims=32)]                    # two value columns a thread, a ragged last slice
 
 
 @pytest.mark.parametrize("dt", DTYPES)
