@@ -5,9 +5,23 @@ sum and the block's own norm are one launch.  What the branches need of the past
 branch gets its own ``LayerCache``."""
 from __future__ import annotations
 
+import os
+
+import torch
+
 from ..weights.loader import TensorSpec
 from .base import Mixer, build_part, register_part
 from .block import Branches
+
+SIDE_BY_SIDE_STREAMS = os.environ.get("MIE_B200_BRANCH_STREAMS", "1") != "0"
+_side_streams: dict = {}
+
+
+def _side_stream(device):
+    key = str(device)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 class ParallelMixers(Mixer):
@@ -44,7 +58,25 @@ class ParallelMixers(Mixer):
         return names
 
     def forward(self, x, ctx, cache):
-        outs = [b.forward(x, ctx, c) for b, c in zip(self.branches, cache.parts)]
+        if (len(self.branches) == 2 and SIDE_BY_SIDE_STREAMS and x.is_cuda
+                and type(self.branches[0]) is not type(self.branches[1])):      # two of a kind would share their kernels' scratch
+            # The branches depend on nothing of one another: the second runs on a stream of its own between a fork and a
+            # join (events; inside a captured step they become two arms of the graph).  A decode step is a chain of
+            # short kernels, and two chains of five side by side take the time of one.  Every tensor either branch
+            # makes is used by the main stream only after the join, and the side stream starts only after the fork,
+            # so the allocator's per-stream reuse stays ordered.
+            main, side = torch.cuda.current_stream(), _side_stream(x.device)
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                second = self.branches[1].forward(x, ctx, cache.parts[1])
+                join.record(side)
+            first = self.branches[0].forward(x, ctx, cache.parts[0])
+            main.wait_event(join)
+            outs = [first, second]
+        else:
+            outs = [b.forward(x, ctx, c) for b, c in zip(self.branches, cache.parts)]
         return Branches(outs, self.out_weights, coef=1.0 / len(outs))
 
 
