@@ -95,3 +95,24 @@ def test_needs_of_a_mixer_made_of_two():
     assert lay.composite == {1: 2, 2: 2} and lay.kv[(1, 0)][0] == 0 and lay.kv[3][0] == 1
     assert set(lay.state) == {0, (1, 1), (2, 1)}
     assert KVNeed(2, 16, None, 20).mask() == -20 and KVNeed(2, 16, 8).mask() == 8 and KVNeed(2, 16).mask() == 0
+
+
+def test_preset_and_the_benchmark_pair_of_equal_size():
+    """The shipped tiny preset reads back, and bench.py's --design option builds a Getizen and a Llama configuration of
+    the same width, feed-forward, heads and number of layers."""
+    import importlib.util
+
+    from mini_inference_engine_b200.config import load_preset, preset_names
+    assert "tiny-getizen" in preset_names()
+    cfg = load_preset("tiny-getizen")
+    assert [l["type"] for l in cfg.layers] == ["parallel", "retention", "parallel"] and cfg.norm_groups == 3
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for size in bench.DESIGN_SIZES.values():
+        g, l = bench.design_configs(size)
+        assert g.width == l.hidden_size == size["width"] and len(g.layers) == l.num_hidden_layers == size["layers"]
+        par = next(x for x in g.layers if x["type"] == "parallel")
+        assert par["mlp"]["ff"] == l.intermediate_size and par["mixer"]["left"]["heads"] == l.num_attention_heads
+        assert par["mixer"]["left"]["kv_heads"] == l.num_key_value_heads and par["mixer"]["left"]["dim"] == l.head_dim
