@@ -490,6 +490,8 @@ def run_design(args, steps, warmup):
             res = entry[label] = {"weight_bytes": eng.model.weight_bytes()}
             if args.kernel_table:
                 from mini_inference_engine_b200 import SamplingParams
+                from mini_inference_engine_b200.parts import parallel
+                parallel.SIDE_BY_SIDE_STREAMS = False        # one stream: a kernel's events then bracket that kernel alone
                 with KernelTimes() as kt:
                     prefill_point(eng, args.prefill_tokens, 1, 2)
                     kt.by_name()
@@ -539,7 +541,8 @@ def main():
                          "layer sizes (--sizes), random weights; decode batches from --points")
     ap.add_argument("--sizes", default="w2048,w4096", help="with --design: layer sizes to measure, of " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--kernel-table", action="store_true",
-                    help="with --design: device time of every kernel of one prompt step and one decode step (run with MIE_B200_PDL=0)")
+                    help="with --design: device time of every kernel of one prompt step and one decode step, all on one stream "
+                         "(run with MIE_B200_PDL=0, so that no kernel starts under its neighbour)")
     args = ap.parse_args()
 
     if args.design:
