@@ -84,19 +84,20 @@ extern "C" int mie_swiglu(const void* gu, void* out, int act_tag, int num_tokens
     return MIE_ERR_BAD_ARG;
 }
 
-// A gated feed-forward activation with clamps, on a fused projection [gate | up] (gate first, `inter` columns each):
+// A gated feed-forward activation with clamps, on a fused projection [gate | up] (gate first, `inter` columns each; with
+// `interleaved`, columns alternate gate_i, up_i as for SwiGLU above):
 //   g = min(gate, limit), u = clamp(up, -limit, limit);  out = g * sigmoid(slope * g) * (u + shift)
 // computed in float32 and rounded once.  limit <= 0 means no clamp.
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int inter, float limit,
-                                   float slope, float shift) {
+                                   float slope, float shift, int interleaved) {
     pdl_enter();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / inter;
         const int i = (int)(idx - t * inter);
-        float g = to_f32<T>(gu[t * 2 * inter + i]);
-        float u = to_f32<T>(gu[t * 2 * inter + inter + i]);
+        float g = to_f32<T>(gu[t * 2 * inter + (interleaved ? 2 * i : i)]);
+        float u = to_f32<T>(gu[t * 2 * inter + (interleaved ? 2 * i + 1 : inter + i)]);
         if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
         out[idx] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
     }
@@ -104,20 +105,30 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
 
 // Eight outputs a thread with 16-byte accesses (bfloat16, inter % 8 == 0)
 __global__ void glu_clamped_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int64_t total8, int inter8,
-                                          float limit, float slope, float shift) {
+                                          float limit, float slope, float shift, int interleaved) {
     pdl_enter();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = idx / inter8;
         const int i8 = (int)(idx - t * inter8);
         const bf16* row = gu + t * 16 * inter8;
-        const uint4 a = *reinterpret_cast<const uint4*>(row + 8 * i8), b = *reinterpret_cast<const uint4*>(row + 8 * inter8 + 8 * i8);
+        // concatenated: a holds eight gates, b eight values; interleaved: a and b hold (gate, value) pairs 0 - 3 and 4 - 7
+        const uint4 a = *reinterpret_cast<const uint4*>(row + (interleaved ? 16 : 8) * i8);
+        const uint4 b = *reinterpret_cast<const uint4*>(row + (interleaved ? 16 * i8 + 8 : 8 * inter8 + 8 * i8));
         const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
         const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
         uint4 o;
         __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            float2 g = __bfloat1622float2(ha[j]), u = __bfloat1622float2(hb[j]);
+            float2 g, u;
+            if (interleaved) {
+                const float2 p0 = __bfloat1622float2(j < 2 ? ha[2 * j] : hb[2 * j - 4]), p1 = __bfloat1622float2(j < 2 ? ha[2 * j + 1] : hb[2 * j - 3]);
+                g = make_float2(p0.x, p1.x);
+                u = make_float2(p0.y, p1.y);
+            } else {
+                g = __bfloat1622float2(ha[j]);
+                u = __bfloat1622float2(hb[j]);
+            }
             if (limit > 0.f) {
                 g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
                 u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
@@ -130,7 +141,7 @@ __global__ void glu_clamped_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __r
 }
 
 extern "C" int mie_glu_clamped(const void* gu, void* out, int act_tag, int num_tokens, int inter, float limit, float slope,
-                               float shift, cudaStream_t stream) {
+                               float shift, int interleaved, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (inter <= 0) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)num_tokens * inter;
@@ -139,14 +150,14 @@ extern "C" int mie_glu_clamped(const void* gu, void* out, int act_tag, int num_t
         int64_t blocks8 = (total / 8 + threads - 1) / threads;
         if (blocks8 > device_sm_count() * 16) blocks8 = device_sm_count() * 16;
         return launch_kernel(glu_clamped_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out,
-                             total / 8, inter / 8, limit, slope, shift);
+                             total / 8, inter / 8, limit, slope, shift, interleaved);
     }
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
     if (act_tag == MIE_F32)
-        return launch_kernel(glu_clamped_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inter, limit, slope, shift);
+        return launch_kernel(glu_clamped_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)gu, (float*)out, total, inter, limit, slope, shift, interleaved);
     else if (act_tag == MIE_BF16)
-        return launch_kernel(glu_clamped_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out, total, inter, limit, slope, shift);
+        return launch_kernel(glu_clamped_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)gu, (bf16*)out, total, inter, limit, slope, shift, interleaved);
     return MIE_ERR_BAD_ARG;
 }
 

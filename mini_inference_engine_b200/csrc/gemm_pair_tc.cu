@@ -44,6 +44,7 @@ struct GpParams {
     void* out;               // [M, N] (or [M, N / 2] with SwiGLU), bfloat16 or float32
     const void* bias;        // [N] or null
     int bias_tag, out_f32, swiglu;
+    float glu_limit, glu_slope, glu_shift;   // the gated epilogue's shape: g' sigmoid(slope g') (u' + shift) with clamps at +-limit (<= 0: none); 0, 1, 0 is SwiGLU
     int M, N, K;
     int tiles_m, num_tiles, k_tiles, stages;
     int* error;
@@ -241,8 +242,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     float o[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float g = v[2 * i], u = v[2 * i + 1];
-                        o[i] = __fdividef(g, 1.f + __expf(-g)) * u;
+                        float g = v[2 * i], u = v[2 * i + 1];
+                        if (p.glu_limit > 0.f) { g = fminf(g, p.glu_limit); u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit); }
+                        o[i] = __fdividef(g, 1.f + __expf(-p.glu_slope * g)) * (u + p.glu_shift);
                     }
                     const int64_t at = (int64_t)row * (p.N / 2) + col / 2;
                     if (p.out_f32) {
@@ -327,7 +329,8 @@ extern "C" int mie_gemm_pair_slots(int N) { return (N + 2 * GP_BNH - 1) / (2 * G
 // xw_out [M, N] bfloat16 and sq_out [mie_gemm_pair_slots(N)][sq_stride >= M] float32.  With fuse->sq_in
 // [sq_slots][sq_in_stride >= M] the sums are scaled by rsqrt(sum over slots / sq_width + sq_eps) first.
 extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
-                             int K, int swiglu, const GpFuse* fuse, cudaStream_t stream) {
+                             int K, int swiglu, float glu_limit, float glu_slope, float glu_shift, const GpFuse* fuse,
+                             cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
     const bool into_stream = fuse && fuse->res;
@@ -346,6 +349,7 @@ extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int
     if ((rc = make_map_rows(&mw, w, N, K))) return rc;
     GpParams p;
     p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.out_f32 = y_tag == MIE_F32; p.swiglu = swiglu ? 1 : 0;
+    p.glu_limit = glu_limit; p.glu_slope = glu_slope; p.glu_shift = glu_shift;
     p.M = M; p.N = N; p.K = K;
     p.tiles_m = (M + 2 * GP_BM - 1) / (2 * GP_BM);
     p.num_tiles = p.tiles_m * ((N + 2 * GP_BNH - 1) / (2 * GP_BNH));

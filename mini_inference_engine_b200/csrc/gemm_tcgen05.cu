@@ -77,7 +77,9 @@ struct TcParams {
     int M, N, K;             // tokens, output features (rows of W), inner size
     int k_tiles, tiles_per_split, splits, stages;
     int l2_ahead;            // weight k-tiles beyond the ring that the copy warp asks into L2 before the dependency wait
-    int swiglu;              // 1: rows 2i / 2i+1 of W are gate_i / up_i; the output is silu(gate) * up, N/2 wide
+    int swiglu;              // 1: rows 2i / 2i+1 of W are gate_i / up_i; the output is glu(gate, up), N/2 wide
+    float glu_limit, glu_slope, glu_shift;   // glu(g, u) = g' sigmoid(slope g') (u' + shift), g' = min(g, limit), u' = clamp(u, +-limit)
+                                             // (limit <= 0: no clamp); 0, 1, 0 is SwiGLU
     // Optional fused rotation + cache write for a q|k|v projection (see the header comment): rows of W
     // are [heads*D of q | kv_heads*D of k | kv_heads*D of v]; q is rotated and written to `out`, k is
     // rotated and v copied into their cache pages at slots[token]; the k and v columns of `out` are not
@@ -131,9 +133,13 @@ __device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, i
 
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// silu(g) * u with the fast exponential and division (a few ulp; the result is rounded to bfloat16 or
+// the gated epilogue g sigmoid(slope g) (u + shift), clamped, with the fast exponential and division (a few ulp; the result is rounded to bfloat16 or
 // added to float32 sums of bfloat16 products)
-__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float glu_mul(float g, float u, float limit, float slope, float shift) {
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    return __fdividef(g, 1.0f + __expf(-slope * g)) * (u + shift);
+}
+#define GLU_OF(g, u) glu_mul(g, u, p.glu_limit, p.glu_slope, p.glu_shift)      // inside a kernel whose parameters are `p`
 
 template <int BN, bool SWAPPED, bool OUT_F32>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -426,7 +432,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         if (p.swiglu) {
                             float h[16];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) h[i] = silu_mul(v[2 * i], v[2 * i + 1]);
+                            for (int i = 0; i < 8; ++i) h[i] = GLU_OF(v[2 * i], v[2 * i + 1]);
 #pragma unroll
                             for (int i = 8; i < 16; ++i) h[i] = 0.f;
                             // 8 outputs starting at column n / 2 of a row N / 2 wide
@@ -455,7 +461,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         if (p.swiglu) {                        // gate on the even lane, up on the odd one
                             const float other = __shfl_xor_sync(0xffffffffu, val, 1);
                             if (!(lane & 1) && t < p.M && n < p.N)
-                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, GLU_OF(val, other));
                         } else if (t < p.M && n < p.N) {
                             store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                         }
@@ -579,7 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                     const float val = acc[j] + b;
                     if (p.swiglu) {                            // gate on the even row, up on the odd one: neighbouring lanes
                         const float other = __shfl_xor_sync(0xffffffffu, val, 1);
-                        if (!(r & 1) && t < p.M && live) store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                        if (!(r & 1) && t < p.M && live) store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, GLU_OF(val, other));
                     } else if (t < p.M && live) {
                         store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                     }
@@ -619,8 +625,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         for (int j = 0; j < 4; ++j) acc[j] += load_tagged(p.bias, n + j, p.bias_tag);
                     }
                     if (p.swiglu) {
-                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2, silu_mul(acc[0], acc[1]));
-                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2 + 1, silu_mul(acc[2], acc[3]));
+                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2, GLU_OF(acc[0], acc[1]));
+                        store_out<OUT_F32>(p.out, (int64_t)m * (p.N / 2) + n / 2 + 1, GLU_OF(acc[2], acc[3]));
                     } else {
 #pragma unroll
                         for (int j = 0; j < 4; ++j) store_out<OUT_F32>(p.out, (int64_t)m * p.N + n + j, acc[j]);
@@ -732,7 +738,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a,     // the 128-row ope
                         if (p.swiglu) {                        // gate on the even feature, up on the odd one: neighbouring threads
                             const float other = __shfl_xor_sync(0xffffffffu, val, 1);
                             if (!(rr & 1) && t < p.M && n < p.N)
-                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, silu_mul(val, other));
+                                store_out<OUT_F32>(p.out, (int64_t)t * (p.N / 2) + n / 2, GLU_OF(val, other));
                         } else if (t < p.M && n < p.N) {
                             store_out<OUT_F32>(p.out, (int64_t)t * p.N + n, val);
                         }
@@ -852,7 +858,8 @@ struct TcFuse {
 
 static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, const RopeFuseArgs* rope,
-                          cudaStream_t stream, const TcFuse* fuse = nullptr) {
+                          cudaStream_t stream, const TcFuse* fuse = nullptr, float glu_limit = 0.f, float glu_slope = 1.f,
+                          float glu_shift = 0.f) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(y)) & 15) return MIE_ERR_BAD_ARG;
@@ -864,6 +871,7 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
     TcParams p;
     p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.error = g_error_dev;
     p.M = M; p.N = N; p.K = K; p.swiglu = swiglu;
+    p.glu_limit = glu_limit; p.glu_slope = glu_slope; p.glu_shift = glu_shift;
     p.res = nullptr; p.norm_w = nullptr; p.norm_w_tag = 0; p.xw_out = nullptr; p.sq_out = nullptr; p.sq_stride = 0;
     p.sq_in = nullptr; p.sq_slots = 0; p.sq_in_stride = 0; p.sq_width = 1.f; p.sq_eps = 0.f;
     if (fuse) {
@@ -940,8 +948,10 @@ static int gemm_tc_launch(const void* x, const void* w, const void* bias, int bi
 }
 
 extern "C" int mie_gemm_tc(const void* x, const void* w, const void* bias, int bias_tag, void* y, int y_tag, int M, int N,
-                           int K, int swapped, int bn, int splits, int stages, int swiglu, int pdl, cudaStream_t stream) {
-    return gemm_tc_launch(x, w, bias, bias_tag, y, y_tag, M, N, K, swapped, bn, splits, stages, swiglu, pdl, nullptr, stream);
+                           int K, int swapped, int bn, int splits, int stages, int swiglu, float glu_limit, float glu_slope,
+                           float glu_shift, int pdl, cudaStream_t stream) {
+    return gemm_tc_launch(x, w, bias, bias_tag, y, y_tag, M, N, K, swapped, bn, splits, stages, swiglu, pdl, nullptr, stream,
+                          nullptr, glu_limit, glu_slope, glu_shift);
 }
 
 // The q|k|v projection with the rotation and the cache write in its epilogue: y [M, N] bfloat16

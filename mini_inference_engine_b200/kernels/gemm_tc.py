@@ -294,10 +294,15 @@ def gemm_residual(x, w: torch.Tensor, res: torch.Tensor, bias=None, norm_weight=
     return out
 
 
-def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, **force) -> torch.Tensor:
+SWIGLU = (0.0, 1.0, 0.0)       # the gated epilogue's (limit, slope, shift) that make it silu(gate) * up
+
+
+def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False, glu=None, **force) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) with bfloat16 operands on tcgen05.  With ``swiglu`` the
-    rows of ``w`` are gate/up interleaved and out is [M, N/2] = silu(gate) * up.  ``x`` may be a
-    DeferredNorm (sizes must then satisfy ``splits_k``)."""
+    rows of ``w`` are gate/up interleaved and out is [M, N/2] = silu(gate) * up -- or, with ``glu`` =
+    (limit, slope, shift), g sigmoid(slope g) (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)
+    (limit <= 0: no clamp).  ``x`` may be a DeferredNorm (sizes must then satisfy ``splits_k``)."""
+    glu = tuple(float(v) for v in (glu or SWIGLU))
     deferred = x if isinstance(x, DeferredNorm) else None
     if deferred is not None:
         x = deferred.xw
@@ -311,6 +316,8 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False,
     pl = plan(M, N, K)
     pl.update(force)
     if deferred is not None:
+        if glu != SWIGLU:
+            raise GemmTcError("the epilogue that takes a deferred norm factor is SwiGLU only")
         if not pl["swapped"]:
             raise GemmTcError("a deferred norm factor needs few tokens and a split K")
         _launch_fused(x, w, bias, out, M, N, K, pl, swiglu, _fuse_struct(deferred), keep=(deferred.sq,),
@@ -319,7 +326,8 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, bias=None, swiglu: bool = False,
     lib = ops.load("gemm_tcgen05")
     rc = lib.mie_gemm_tc(ops._ptr(x), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                          ops._ptr(out), ops.tag(out), M, N, K, int(pl["swapped"]), pl["bn"], pl["splits"], pl["stages"],
-                         int(swiglu), int(pl.get("pdl", pdl_enabled)), ops._stream())
+                         int(swiglu), ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]),
+                         int(pl.get("pdl", pdl_enabled)), ops._stream())
     ops._check(rc, f"gemm_tc M{M} N{N} K{K} {pl}")
     return out
 
@@ -380,13 +388,14 @@ def pair_supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
 
 
 def gemm_pair(x, w: torch.Tensor, out: torch.Tensor | None, bias: torch.Tensor | None = None, swiglu: bool = False,
-              res: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0):
+              res: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0, glu=None):
     """out = x w^T (+ bias), or silu(gate) * value over interleaved rows of ``w`` with ``swiglu``: the product
     for many tokens on pairs of SMs (``csrc/gemm_pair_tc.cu``: 256 x 256 tiles by cta_group::2 MMAs, two
     accumulators in tensor memory, one persistent pair of blocks per two SMs).  ``x`` may be a DeferredNorm (the
     norm in front becomes a row factor on the sums).  With ``res`` (float32 [M, N]) the product is added to it
     in place instead of being written (``out`` is None); with ``norm_weight`` as well, the DeferredNorm for the
     product behind that norm is returned."""
+    glu = tuple(float(v) for v in (glu or SWIGLU))        # the gated epilogue's shape, as for ``gemm``
     deferred = x if isinstance(x, DeferredNorm) else None
     xt = deferred.xw if deferred is not None else x
     M, K = xt.shape
@@ -410,6 +419,7 @@ def gemm_pair(x, w: torch.Tensor, out: torch.Tensor | None, bias: torch.Tensor |
     fuse = _fuse_struct(deferred, res, norm_weight, xw, sq)
     ops._check(lib.mie_gemm_pair(ops._ptr(xt), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
                                  ops._ptr(out), ops.tag(out) if out is not None else 0, M, N, K, int(swiglu),
+                                 ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]),
                                  ctypes.byref(fuse), ops._stream()), "gemm_pair")
     return made if res is not None else out
 

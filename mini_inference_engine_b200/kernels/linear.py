@@ -137,13 +137,23 @@ def linear(x, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
-def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype, glu=None) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for a weight whose rows alternate gate_i, up_i: fused into the
-    tcgen05 product's epilogue where that kernel runs, else the product followed by the SwiGLU kernel."""
+    tcgen05 product's epilogue where that kernel runs, else the product followed by the SwiGLU kernel.
+    ``glu`` = (limit, slope, shift) makes the gate g sigmoid(slope g) (u + shift) with g = min(gate, limit),
+    u = clamp(up, -limit, limit) instead (the same epilogues with other constants, the clamped kernel else)."""
     M, inter = x.shape[0], w_interleaved.shape[0] // 2
     out = torch.empty(M, inter, dtype=out_dtype, device=w_interleaved.device)
     if M == 0:
         return out
+    if glu is not None:
+        if (takes_pair(M, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and x.dtype == torch.bfloat16
+                and out_dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()):
+            return gemm_tc.gemm_pair(x, w_interleaved, out, swiglu=True, glu=glu)
+        if uses_tcgen05(x, w_interleaved) and w_interleaved.shape[0] % 16 == 0 and gemm_tc.supports(x, w_interleaved, out):
+            return gemm_tc.gemm(x, w_interleaved, out, swiglu=True, glu=glu)
+        gu = linear(x, w_interleaved, None, out_dtype)
+        return ops.glu_clamped(gu, out, glu[0], glu[1], glu[2], interleaved=True)
     if isinstance(x, gemm_tc.DeferredNorm):
         if w_interleaved.shape[0] % 16 == 0:
             return gemm_tc.gemm(x, w_interleaved, out, swiglu=True)

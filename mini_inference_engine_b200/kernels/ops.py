@@ -718,15 +718,17 @@ def recurrence_scan(a, b, y, x, row_q_start, row_q_len, state_slots, state, out,
 
 # --------------------------------------------------------------------------- gated activations
 
-def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float) -> torch.Tensor:
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, limit: float, slope: float, shift: float,
+                interleaved: bool = False) -> torch.Tensor:
     """out = g * sigmoid(slope * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit) from the
-    fused projection [gate | up]; ``limit`` <= 0 leaves both unclamped."""
+    fused projection [gate | up] (with ``interleaved``: columns gate_0, up_0, gate_1, ...); ``limit`` <= 0 leaves both
+    unclamped."""
     T, two_i = gate_up.shape
     _need(two_i % 2 == 0 and out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype
           and out.is_contiguous() and gate_up.is_contiguous(), "glu shapes/types do not match")
     lib = build.load("activation")
     _check(lib.mie_glu_clamped(_ptr(gate_up), _ptr(out), tag(out), T, two_i // 2, ctypes.c_float(limit), ctypes.c_float(slope),
-                               ctypes.c_float(shift), _stream()), "glu_clamped")
+                               ctypes.c_float(shift), int(interleaved), _stream()), "glu_clamped")
     return out
 
 

@@ -61,8 +61,9 @@ register_part("feed_forward", "swiglu", SwiGLU)
 
 class ClampedGLU(FeedForward):
     """A gated feed-forward with clamps: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
-    output W_down (g sigmoid(slope g) (u + shift)).  gate and up are one product ([gate | up] by concatenation);
-    the activation is one kernel in float32; the last product leaves float32 for the stream's sum."""
+    output W_down (g sigmoid(slope g) (u + shift)).  gate and up are one product; in bfloat16 the tensor-core
+    products apply the gate to their float32 sums in the epilogue (rows interleaved, as for SwiGLU), elsewhere one
+    kernel does in float32; the last product leaves float32 for the stream's sum."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702, shift: float = 1.0):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -77,16 +78,25 @@ class ClampedGLU(FeedForward):
         g, u = tensors["gate"], tensors["up"]
         if g.dtype != u.dtype:
             g, u = g.float(), u.float()
-        self.w_gate_up = rt.place(torch.cat([g, u], 0))
+        # in bfloat16 the rows alternate gate_i, up_i, as for SwiGLU: the tensor-core products then apply the gate in
+        # their epilogue (the same epilogue with this part's constants)
+        self.interleaved = rt.dtype == torch.bfloat16 and g.dtype != torch.float32
+        if self.interleaved:
+            self.w_gate_up = rt.place(torch.stack((g, u), 1).reshape(2 * self.intermediate_size, self.hidden_size))
+        else:
+            self.w_gate_up = rt.place(torch.cat([g, u], 0))
         self.w_down = rt.place(tensors["down"])
 
     def kernel_sources(self):
         return {"activation"} | self.rt.product_sources(self.w_gate_up, self.w_down)
 
     def forward(self, x, ctx):
-        gu = self.rt.linear(x, self.w_gate_up)
-        act = self.rt.empty(x.shape[0], self.intermediate_size)
-        ops.glu_clamped(gu, act, self.limit, self.slope, self.shift)
+        if self.interleaved:
+            act = linear_kernels.linear_swiglu(x, self.w_gate_up, self.rt.dtype, glu=(self.limit, self.slope, self.shift))
+        else:
+            gu = self.rt.linear(x, self.w_gate_up)
+            act = self.rt.empty(x.shape[0], self.intermediate_size)
+            ops.glu_clamped(gu, act, self.limit, self.slope, self.shift)
         return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)
 
 
