@@ -5,6 +5,7 @@ The reference has no registry (inference_engine/engine.py:44 builds Llama for an
 from __future__ import annotations
 
 from .getizen_config import GetizenConfig
+from .kebudra_config import KebudraConfig
 from .model_config import ConfigError, LlamaConfig, read_config_json
 
 _ARCHITECTURES: dict[str, type] = {}
@@ -40,6 +41,7 @@ def load_config(path_or_dict):
 
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Getizen", GetizenConfig)
+register_architecture("Kebudra", KebudraConfig)
 
 
 def preset_names() -> list[str]:

@@ -1,0 +1,261 @@
+// The gated delta rule with one decay per head and key channel: a linear-attention mixer whose per-head state
+// S [D, Dv] (float32) forgets per key channel, corrects what it holds under the new key, and is read by the query:
+//
+//   S <- diag(g_t) S;   u = beta_t (v_t - S^T k_t);   S <- S + k_t u^T;   o_t = S^T q_t        (in this order)
+//
+// Three kernels:
+//   prepare    per token: the short causal convolution over time of q, k and v (inputs older than the step's portion come
+//              from the request's convolution state), silu, q and k made unit vectors per head (q also scaled), beta =
+//              sigmoid of its logit, g = exp(-exp(A_log[h]) softplus(a + dt_bias)) -- all float32;
+//   conv_state the last K - 1 inputs of the convolution of every row move into its state slot (after prepare has read it);
+//   scan       the recurrence, token by token per row, one block per (row, head, slice of value columns): a group of L
+//              lanes owns one column of S (D / L entries each, in registers), so S is read from memory once per step and
+//              written once.  The read-out uses S after the token's own write:
+//              o = (g S)^T q + u (k . q), which needs one pass over the column for both sums.
+//   head_norm_gate   o / rms(o) per head, times a weight shared by the heads, times sigmoid of a gate logit.
+//
+// State layouts: S [slot, H, Dv, D] float32 (a column of S contiguous); convolution [slot, K - 1, C] float32 with row i the
+// input at K - 1 - i tokens before the next one.  Slot 0 is scratch.
+#include "common.cuh"
+
+#define DELTA_R 16          // entries of a column a lane holds
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// The convolution's output for channel c (of C) at token t: taps [C, K], last tap on the token itself.
+template <typename T>
+__device__ __forceinline__ float conv_at(const T* __restrict__ x, int64_t stride, const float* __restrict__ taps,
+                                         const float* __restrict__ st, int C, int K, int t, int local, int c) {
+    float acc = 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int back = K - 1 - j;                 // how many tokens before t
+        const float xv = back <= local ? to_f32<T>(x[(int64_t)(t - back) * stride + c])
+                                       : st[(int64_t)(K - 1 - (back - local)) * C + c];
+        acc = fmaf(taps[(int64_t)c * K + j], xv, acc);
+    }
+    return acc / (1.0f + expf(-acc));
+}
+
+// proj[t] = [ q: G x D | k: G x D | v: H x Dv | beta logits: H | ... ] (activation type, row stride `stride`);
+// low[t] = [ a: H x D | ... ] float32 (row stride low_stride).  One block per token, one warp per head of q, k or v.
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ proj, int64_t stride, const float* __restrict__ low, int64_t low_stride,
+                                     const float* __restrict__ taps, const float* __restrict__ conv_state,
+                                     const int* __restrict__ token_row, const int* __restrict__ row_q_start,
+                                     const int* __restrict__ state_slots, const float* __restrict__ a_log,
+                                     const float* __restrict__ dt_bias, float* __restrict__ qn, float* __restrict__ kn,
+                                     float* __restrict__ vn, float* __restrict__ beta, float* __restrict__ decay, int H, int G,
+                                     int D, int Dv, int K, float q_scale, float unit_eps) {
+    pdl_enter();
+    const int t = blockIdx.x;
+    const int row = token_row[t];
+    const int local = t - row_q_start[row];
+    const int C = 2 * G * D + H * Dv;
+    const float* st = conv_state + (int64_t)state_slots[row] * (K - 1) * C;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int unit = warp; unit < 2 * G + H; unit += nw) {
+        const bool is_v = unit >= 2 * G;
+        const int n = is_v ? Dv : D;
+        const int c0 = is_v ? 2 * G * D + (unit - 2 * G) * Dv : unit * D;
+        float* dst = is_v ? vn + (int64_t)t * H * Dv + (unit - 2 * G) * Dv
+                          : (unit < G ? qn + (int64_t)t * G * D + unit * D : kn + (int64_t)t * G * D + (unit - G) * D);
+        if (is_v) {
+            for (int d = lane; d < n; d += 32) dst[d] = conv_at<T>(proj, stride, taps, st, C, K, t, local, c0 + d);
+        } else {
+            float ss = 0.f;
+            for (int d = lane; d < n; d += 32) {
+                const float y = conv_at<T>(proj, stride, taps, st, C, K, t, local, c0 + d);
+                dst[d] = y;
+                ss += y * y;
+            }
+            const float s = (unit < G ? q_scale : 1.0f) / sqrtf(warp_sum(ss) + unit_eps);
+            for (int d = lane; d < n; d += 32) dst[d] *= s;           // the lane's own entries
+        }
+    }
+    const T* bl = proj + (int64_t)t * stride + C;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) beta[(int64_t)t * H + h] = 1.0f / (1.0f + expf(-to_f32<T>(bl[h])));
+    for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
+        const float rate = expf(a_log[i / D]);
+        decay[(int64_t)t * H * D + i] = expf(-rate * softplus_f(low[(int64_t)t * low_stride + i] + dt_bias[i]));
+    }
+}
+
+// The convolution state of every row after the step: row i of the new state is the input at q_len - (K - 1) + i of the
+// portion, or, where the portion is shorter than that reaches back, a row of the old state.  One thread per channel
+// walks the rows upwards, so the move is safe in place.
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ x, int64_t stride, const int* __restrict__ row_q_start,
+                                  const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
+                                  float* __restrict__ conv_state, int C, int K) {
+    pdl_enter();
+    const int row = blockIdx.y;
+    const int slot = state_slots[row];
+    const int q0 = row_q_start[row], n = row_q_len[row];
+    float* st = conv_state + (int64_t)slot * (K - 1) * C;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < C; c += gridDim.x * blockDim.x) {
+        for (int i = 0; i < K - 1; ++i) {
+            const int li = n - (K - 1) + i;
+            st[(int64_t)i * C + c] = li >= 0 ? to_f32<T>(x[(int64_t)(q0 + li) * stride + c]) : st[(int64_t)(i + n) * C + c];
+        }
+    }
+}
+
+__global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn,
+                                  const float* __restrict__ beta, const float* __restrict__ decay,
+                                  const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
+                                  const int* __restrict__ state_slots, float* __restrict__ state, float* __restrict__ out, int H,
+                                  int G, int D, int Dv, int L, int cols) {
+    pdl_enter();
+    const int row = blockIdx.x, h = blockIdx.y;
+    const int l = threadIdx.x % L, j = blockIdx.z * cols + threadIdx.x / L;
+    const bool active = (int)(threadIdx.x / L) < cols && j < Dv;      // threads that only fill up the last warp own no column
+    const int n = row_q_len[row], t0 = row_q_start[row];
+    const int kh = h / (H / G);
+    float* sp = state + (((int64_t)state_slots[row] * H + h) * Dv + (active ? j : 0)) * D;
+    float s[DELTA_R];
+#pragma unroll
+    for (int r = 0; r < DELTA_R; ++r) {
+        const int i = l + L * r;
+        s[r] = (active && i < D) ? sp[i] : 0.f;
+    }
+    float nk[DELTA_R], nq[DELTA_R], ng[DELTA_R], nv = 0.f, nb = 0.f;
+    auto fetch = [&](int t) {
+        const float* kp = kn + ((int64_t)t * G + kh) * D;
+        const float* qp = qn + ((int64_t)t * G + kh) * D;
+        const float* gp = decay + ((int64_t)t * H + h) * D;
+#pragma unroll
+        for (int r = 0; r < DELTA_R; ++r) {
+            const int i = l + L * r;
+            const bool ok = i < D;
+            nk[r] = ok ? kp[i] : 0.f;
+            nq[r] = ok ? qp[i] : 0.f;
+            ng[r] = ok ? gp[i] : 0.f;
+        }
+        nv = active ? vn[((int64_t)t * H + h) * Dv + j] : 0.f;
+        nb = beta[(int64_t)t * H + h];
+    };
+    if (n > 0) fetch(t0);
+    for (int tok = 0; tok < n; ++tok) {
+        const int t = t0 + tok;
+        float k[DELTA_R], q[DELTA_R];
+        float r1 = 0.f, r2 = 0.f, kq = 0.f;
+        const float v = nv, b = nb;
+#pragma unroll
+        for (int r = 0; r < DELTA_R; ++r) {
+            k[r] = nk[r];
+            q[r] = nq[r];
+            s[r] *= ng[r];
+            r1 = fmaf(s[r], k[r], r1);
+            r2 = fmaf(s[r], q[r], r2);
+            kq = fmaf(k[r], q[r], kq);
+        }
+        if (tok + 1 < n) fetch(t + 1);              // the next token's operands travel while this one is reduced
+        for (int o = L >> 1; o > 0; o >>= 1) {
+            r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+            r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+            kq += __shfl_xor_sync(0xffffffffu, kq, o);
+        }
+        const float u = b * (v - r1);
+#pragma unroll
+        for (int r = 0; r < DELTA_R; ++r) s[r] = fmaf(k[r], u, s[r]);
+        if (active && l == 0) out[((int64_t)t * H + h) * Dv + j] = fmaf(u, kq, r2);
+    }
+    if (active) {
+#pragma unroll
+        for (int r = 0; r < DELTA_R; ++r) {
+            const int i = l + L * r;
+            if (i < D) sp[i] = s[r];
+        }
+    }
+}
+
+// out[t, h, :] = o[t, h, :] * rsqrt(mean(o[t, h, :]^2) + eps) * w[:] * sigmoid(gate[t, h, :]); a warp per (token, head).
+// gate: float32 rows of stride gate_stride; w: float32 [Dv] or null.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, int64_t gate_stride,
+                                      const float* __restrict__ w, T* __restrict__ out, int num_tokens, int H, int Dv, float eps) {
+    pdl_enter();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)num_tokens * H) return;
+    const int64_t t = item / H;
+    const int h = (int)(item - t * H);
+    const float* src = o + item * Dv;
+    float ss = 0.f;
+    for (int i = lane; i < Dv; i += 32) { const float v = src[i]; ss += v * v; }
+    const float s = 1.0f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+    const float* g = gate ? gate + t * gate_stride + (int64_t)h * Dv : nullptr;
+    for (int i = lane; i < Dv; i += 32) {
+        float v = src[i] * s;
+        if (w) v *= w[i];
+        if (g) v /= 1.0f + expf(-g[i]);
+        out[item * Dv + i] = from_f32<T>(v);
+    }
+}
+
+extern "C" int mie_delta_prepare(const void* proj, int tag, long long stride, const float* low, long long low_stride, const float* taps,
+                                 const float* conv_state, const int* token_row, const int* row_q_start, const int* state_slots,
+                                 const float* a_log, const float* dt_bias, float* qn, float* kn, float* vn, float* beta, float* decay,
+                                 int num_tokens, int H, int G, int D, int Dv, int K, float q_scale, float unit_eps,
+                                 cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || K < 1) return MIE_ERR_BAD_ARG;
+    const int units = 2 * G + H;
+    const int threads = units >= 8 ? 256 : (units >= 4 ? 128 : 64);
+    if (tag == MIE_F32)
+        return launch_kernel(delta_prepare_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)proj, (int64_t)stride,
+                             low, (int64_t)low_stride, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias, qn, kn, vn,
+                             beta, decay, H, G, D, Dv, K, q_scale, unit_eps);
+    else if (tag == MIE_BF16)
+        return launch_kernel(delta_prepare_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)proj, (int64_t)stride,
+                             low, (int64_t)low_stride, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias, qn, kn, vn,
+                             beta, decay, H, G, D, Dv, K, q_scale, unit_eps);
+    return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_conv_state_update(const void* x, int tag, long long stride, const int* row_q_start, const int* row_q_len,
+                                     const int* state_slots, float* conv_state, int num_rows, int C, int K, cudaStream_t stream) {
+    if (num_rows <= 0 || K <= 1) return 0;
+    if (C <= 0) return MIE_ERR_BAD_ARG;
+    const int threads = 128;
+    const dim3 grid((C + threads - 1) / threads, num_rows);
+    if (tag == MIE_F32)
+        return launch_kernel(conv_state_kernel<float>, grid, dim3(threads), 0, stream, (const float*)x, (int64_t)stride, row_q_start,
+                             row_q_len, state_slots, conv_state, C, K);
+    else if (tag == MIE_BF16)
+        return launch_kernel(conv_state_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)x, (int64_t)stride, row_q_start,
+                             row_q_len, state_slots, conv_state, C, K);
+    return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
+                              const int* row_q_start, const int* row_q_len, const int* state_slots, float* state, float* out,
+                              int num_rows, int H, int G, int D, int Dv, cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0) return MIE_ERR_BAD_ARG;
+    int L = 1;
+    while (L * DELTA_R < D) L <<= 1;
+    if (L > 32) return MIE_ERR_TOO_LARGE;                      // key sizes beyond 32 x DELTA_R
+    int cols = 128 / L;                                        // value columns a block of 128 threads
+    if (cols > Dv) cols = Dv;
+    const int threads = (cols * L + 31) / 32 * 32;
+    const dim3 grid(num_rows, H, (Dv + cols - 1) / cols);
+    return launch_kernel(delta_scan_kernel, grid, dim3(threads), 0, stream, qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots,
+                         state, out, H, G, D, Dv, L, cols);
+}
+
+extern "C" int mie_head_norm_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out, int tag,
+                                  int num_tokens, int H, int Dv, float eps, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (H <= 0 || Dv <= 0) return MIE_ERR_BAD_ARG;
+    const int warps = 4;
+    const int64_t items = (int64_t)num_tokens * H;
+    const int blocks = (int)((items + warps - 1) / warps);
+    if (tag == MIE_F32)
+        return launch_kernel(head_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o, gate, (int64_t)gate_stride, w,
+                             (float*)out, num_tokens, H, Dv, eps);
+    else if (tag == MIE_BF16)
+        return launch_kernel(head_norm_gate_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, o, gate, (int64_t)gate_stride, w,
+                             (bf16*)out, num_tokens, H, Dv, eps);
+    return MIE_ERR_BAD_ARG;
+}

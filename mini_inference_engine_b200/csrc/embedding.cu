@@ -3,13 +3,15 @@
 // (what F.embedding does at inference_engine/model.py:168).
 // A negative id -(k+1) stands for "the k-th token the previous step sampled": it is read from the
 // `feedback` buffer on the device, so a step can be launched before the host has seen that token.
+// `scale` multiplies the row (in float32) and `copies` writes it that many times side by side (a model that carries
+// several copies of its stream: out is [tokens, copies, hidden]).
 #include "common.cuh"
 #include "range_check.cuh"
 
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  const int* __restrict__ feedback, float* __restrict__ out, int hidden, int vocab,
-                                 int feedback_len, int* report) {
+                                 int feedback_len, float scale, int copies, int* report) {
     pdl_enter();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -22,18 +24,21 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
         return;
     }
     const TT* src = table + (int64_t)id * hidden;
-    float* dst = out + (int64_t)t * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<TT>(src[i]);
+    float* dst = out + (int64_t)t * copies * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_f32<TT>(src[i]) * scale;
+        for (int c = 0; c < copies; ++c) dst[(int64_t)c * hidden + i] = v;
+    }
 }
 
 extern "C" int mie_embedding(const void* table, int table_tag, const int* ids, const int* feedback, float* out,
-                             int num_tokens, int hidden, int vocab, int feedback_len, cudaStream_t stream) {
+                             int num_tokens, int hidden, int vocab, int feedback_len, float scale, int copies, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (hidden <= 0 || vocab <= 0) return MIE_ERR_BAD_ARG;
+    if (hidden <= 0 || vocab <= 0 || copies < 1) return MIE_ERR_BAD_ARG;
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     if (table_tag == MIE_F32)
-        return launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)table, ids, feedback, out, hidden, vocab, feedback_len, g_range_report);
+        return launch_kernel(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)table, ids, feedback, out, hidden, vocab, feedback_len, scale, copies, g_range_report);
     else if (table_tag == MIE_BF16)
-        return launch_kernel(embedding_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, feedback, out, hidden, vocab, feedback_len, g_range_report);
+        return launch_kernel(embedding_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)table, ids, feedback, out, hidden, vocab, feedback_len, scale, copies, g_range_report);
     return MIE_ERR_BAD_ARG;
 }

@@ -35,7 +35,8 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fP
 SOURCES = ("embedding", "norm", "rope_cache", "attention_simt", "attention_decode", "attention_decode_static", "attention_prefill",
            "attention_prefill_tc",
            "activation", "gemm_simt", "gemm_tcgen05", "gemm_chain", "gemm_pair_tc",
-           "sampling", "norm_group", "qk_norm_rope", "retention", "linear_recurrence")
+           "sampling", "norm_group", "qk_norm_rope", "retention", "linear_recurrence",
+           "hyper_norm", "latent_kv", "diff_attention", "delta_rule", "moe")
 
 _libs: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -78,7 +78,7 @@ _RANGE_CODES = {1: "token id outside the vocabulary (or the fed-back tokens)", 2
                 4: "block-table entry outside the page pool", 5: "row index outside the batch"}
 _RANGE_KERNELS = {1: "embedding", 2: "rope_cache", 3: "norm", 4: "attention_simt", 5: "attention_decode",
                   6: "attention_prefill", 7: "attention_prefill_tc", 8: "gemm_tcgen05 (q|k|v with rotation)",
-                  9: "norm_group", 10: "qk_norm_rope"}
+                  9: "norm_group", 10: "qk_norm_rope", 11: "hyper_norm", 12: "latent_kv"}
 _range_report: torch.Tensor | None = None
 _range_told: set = set()
 
@@ -124,19 +124,20 @@ def _i32(t, name):
 
 # --------------------------------------------------------------------------- embedding
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, feedback: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] as float32 (the residual stream).  An id -(k+1) is replaced on the device
-    by ``feedback[k]`` (a token the previous step sampled and the host has not read yet)."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, feedback: torch.Tensor | None = None,
+              scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale as float32 (the residual stream), written ``copies`` times side by side.  An id
+    -(k+1) is replaced on the device by ``feedback[k]`` (a token the previous step sampled and the host has not read yet)."""
     if feedback is not None:
         _i32(feedback, "feedback")
     _i32(ids, "ids")
     V, h = table.shape
-    _need(out.dtype == torch.float32 and out.shape == (ids.numel(), h) and out.is_contiguous(),
-          "embedding output must be contiguous float32 [tokens, hidden]")
+    _need(out.dtype == torch.float32 and out.shape == (ids.numel(), copies * h) and out.is_contiguous(),
+          "embedding output must be contiguous float32 [tokens, copies * hidden]")
     _need(table.is_contiguous(), "embedding table must be contiguous")
     lib = load("embedding")
     _check(lib.mie_embedding(_ptr(table), tag(table), _ptr(ids), _ptr(feedback), _ptr(out), ids.numel(), h, V,
-                             feedback.numel() if feedback is not None else 0, _stream()),
+                             feedback.numel() if feedback is not None else 0, ctypes.c_float(scale), int(copies), _stream()),
            "embedding")
     return out
 
@@ -597,8 +598,9 @@ def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out:
     ``q_out`` [T, H, DP] and k, v to their cache slots (pages [page, G, page_size, DP], tails zero)."""
     T = qkv.shape[0]
     DP = q_out.shape[-1]
-    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= (num_heads + num_kv_heads) * dim + num_kv_heads * vdim,
-          "qkv rows must hold q, k and v")
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1
+          and qkv.shape[1] >= (num_heads * dim + (num_kv_heads * (dim + vdim) if write_cache else 0)),
+          "qkv rows must hold q, k and v (q alone when the cache is not written)")
     _need(q_out.is_contiguous() and q_out.shape == (T, num_heads, DP) and q_out.dtype == qkv.dtype, "q_out must be [T, H, DP]")
     _need(k_cache.dtype == qkv.dtype == v_cache.dtype and k_cache.shape[-1] == DP and k_cache.is_contiguous(), "cache type and width")
     _need(freq.dtype == torch.float32 and freq.numel() * 2 == rot and freq.is_contiguous(), "one float32 frequency per rotated pair")
@@ -747,3 +749,204 @@ def sigmoid_gate(attn: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_
 
 def default_scale(head_dim: int) -> float:
     return 1.0 / math.sqrt(head_dim)
+
+
+# --------------------------------------------------------------------------- hyper-connections, Dynamic Tanh
+
+def _f32(t, name, numel=None):
+    _need(t.dtype == torch.float32 and t.is_contiguous() and (numel is None or t.numel() == numel),
+          f"{name} must be contiguous float32" + (f" with {numel} entries" if numel is not None else ""))
+
+
+def hyper_norm(res: torch.Tensor, streams: int, out: torch.Tensor, *, weight=None, bias=None, alpha=None, y=None, mix=None,
+               out_coef=None, in_coef=None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """One pass over a stream kept in ``streams`` copies, ``res`` [T, streams * W] float32: with a pending sublayer output
+    ``y`` [T, W], x'_r = sum_s mix[s, r] x_s + out_coef[r] y (in place, unless ``rows``); then u = sum_r in_coef[r] x'_r and
+    out = tanh(alpha u) weight + bias (u itself without a weight).  A missing mix / out_coef / in_coef is the identity /
+    ones / ones.  With ``rows`` output row b comes from stream row rows[b] and ``res`` is not written."""
+    T = res.shape[0]
+    S = int(streams)
+    _need(res.dim() == 2 and res.shape[1] % S == 0, "the streams must be [tokens, streams * width]")
+    W = res.shape[1] // S
+    _f32(res, "the streams")
+    for t, name, n in ((weight, "norm weight", W), (bias, "norm bias", W), (alpha, "alpha", 1), (mix, "mix", S * S),
+                       (out_coef, "out coefficients", S), (in_coef, "in coefficients", S)):
+        if t is not None:
+            _f32(t, name, n)
+    _need((weight is None) == (bias is None), "Dynamic Tanh takes a weight and a bias")
+    if y is not None:
+        _need(y.shape == (T, W) and y.is_contiguous(), "a pending output must be contiguous [tokens, width]")
+    num_out = T
+    if rows is not None:
+        _i32(rows, "rows")
+        num_out = rows.numel()
+    _need(out.is_contiguous() and out.shape == (num_out, W), "norm output must be contiguous [rows, width]")
+    lib = load("hyper_norm")
+    _check(lib.mie_hyper_norm(_ptr(res), _ptr(y), tag(y) if y is not None else 0, _ptr(mix), _ptr(out_coef), _ptr(in_coef),
+                              _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out), tag(out), _ptr(rows), num_out, W, S, T,
+                              0 if weight is not None else 1, _stream()), "hyper_norm")
+    return out
+
+
+# --------------------------------------------------------------------------- latent attention
+
+def latent_norm_rope(down: torch.Tensor, positions, freq, q_weight, c_weight, eps: float, cq, c, kr, *, q_rank: int, kv_rank: int,
+                     rot_dim: int, rot: int) -> None:
+    """From rows [dq: q_rank | dkv: kv_rank + rot_dim | ...] of the down-projection: cq = rms(dq) q_weight, c =
+    rms(dkv[:kv_rank]) c_weight (activation type), kr = dkv[kv_rank:] rotated by position x ``freq`` over its first ``rot``
+    entries, entry 2i with 2i + 1 (float32)."""
+    T = down.shape[0]
+    _need(down.dim() == 2 and down.stride(1) == 1 and down.shape[1] >= q_rank + kv_rank + rot_dim, "down-projection rows too short")
+    _f32(q_weight, "query latent norm weight", q_rank)
+    _f32(c_weight, "key/value latent norm weight", kv_rank)
+    _f32(freq, "frequencies", rot // 2)
+    _i32(positions, "positions")
+    _need(cq.shape == (T, q_rank) and c.shape == (T, kv_rank) and cq.dtype == c.dtype == down.dtype and cq.is_contiguous()
+          and c.is_contiguous(), "latents must be contiguous [T, rank] in the activation type")
+    _need(kr.shape == (T, rot_dim) and kr.dtype == torch.float32 and kr.is_contiguous(), "the shared key part must be float32 [T, rot_dim]")
+    lib = load("latent_kv")
+    _check(lib.mie_latent_norm_rope(_ptr(down), tag(down), ctypes.c_longlong(down.stride(0)), _ptr(positions), _ptr(freq),
+                                    _ptr(q_weight), _ptr(c_weight), ctypes.c_float(eps), _ptr(cq), _ptr(c), _ptr(kr), T, q_rank,
+                                    kv_rank, rot_dim, rot, _stream()), "latent_norm_rope")
+
+
+def latent_assemble(qu: torch.Tensor, kvu: torch.Tensor, kr: torch.Tensor, positions, slots, freq, q_out, k_cache, v_cache, *,
+                    num_heads: int, dim: int, rot_dim: int, vdim: int, rot: int, page_size: int, write_cache: bool = True) -> None:
+    """q_out[t, h] = [qu[t, h, :dim] | rotate(qu[t, h, dim:]) | 0]; cache k[h] = [kvu.k[h] | kr | 0], v[h] = [kvu.v[h] | 0]
+    with kvu rows [k: H x dim | v: H x vdim]; heads padded to the pages' width."""
+    T, H, DP = qu.shape[0], num_heads, q_out.shape[-1]
+    _need(qu.is_contiguous() and qu.shape == (T, H * (dim + rot_dim)), "qu must be contiguous [T, H * (dim + rot_dim)]")
+    _need(kvu.is_contiguous() and kvu.shape == (T, H * (dim + vdim)) and kvu.dtype == qu.dtype, "kvu must be contiguous [T, H * (dim + vdim)]")
+    _need(kr.shape == (T, rot_dim) and kr.dtype == torch.float32 and kr.is_contiguous(), "the shared key part must be float32 [T, rot_dim]")
+    _need(q_out.is_contiguous() and q_out.shape == (T, H, DP) and q_out.dtype == qu.dtype, "q_out must be [T, H, DP]")
+    _need(k_cache.dtype == qu.dtype == v_cache.dtype and k_cache.shape[-1] == DP and k_cache.shape[1] == H and k_cache.is_contiguous(),
+          "cache type, heads and width")
+    _f32(freq, "frequencies", rot // 2)
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    lib = load("latent_kv")
+    _check(lib.mie_latent_assemble(_ptr(qu), _ptr(kvu), tag(qu), _ptr(kr), _ptr(positions), _ptr(slots), _ptr(freq), _ptr(q_out),
+                                   _ptr(k_cache), _ptr(v_cache), T, H, dim, rot_dim, vdim, DP, rot, page_size,
+                                   ctypes.c_longlong(k_cache.shape[0]), int(write_cache), _stream()), "latent_assemble")
+
+
+# --------------------------------------------------------------------------- differential attention
+
+def diff_combine(maps: torch.Tensor, gate, out: torch.Tensor, *, num_heads: int, group: int, vdim: int, lam: float, eps: float,
+                 out_scale: float) -> torch.Tensor:
+    """out[t, h] = rmsnorm(a1 - lam a2) out_scale sigmoid(gate[t, h]) with a1, a2 heads (2g) group + i and (2g + 1) group + i of
+    ``maps`` [T, 2H, DP] for h = g group + i; ``gate`` [T, H] may be a column slice (None: no gate)."""
+    T, DP = maps.shape[0], maps.shape[-1]
+    _need(maps.is_contiguous() and maps.shape == (T, 2 * num_heads, DP) and DP >= vdim, "maps must be [T, 2H, DP]")
+    _need(out.is_contiguous() and out.shape == (T, num_heads * vdim) and out.dtype == maps.dtype, "out must be contiguous [T, H * vdim]")
+    if gate is not None:
+        _need(gate.stride(1) == 1 and gate.shape == (T, num_heads) and gate.dtype == maps.dtype, "gate must be [T, H]")
+    lib = load("diff_attention")
+    _check(lib.mie_diff_combine(_ptr(maps), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+                                tag(out), T, num_heads, group, vdim, DP, ctypes.c_float(lam), ctypes.c_float(eps),
+                                ctypes.c_float(out_scale), _stream()), "diff_combine")
+    return out
+
+
+# --------------------------------------------------------------------------- gated delta rule
+
+def delta_prepare(proj: torch.Tensor, low: torch.Tensor, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias,
+                  qn, kn, vn, beta, decay, *, num_heads: int, num_kv_heads: int, dim: int, vdim: int, unit_eps: float) -> None:
+    """From rows [q: G x dim | k: G x dim | v: H x vdim | beta logits: H | ...] of the input projection and float32 rows
+    [a: H x dim | ...] of the low-rank one: convolution over time + silu of q, k, v (float32 taps [channels, K], older inputs
+    from ``conv_state`` [slots, K - 1, channels]), q and k unit vectors per head (q times dim^-1/2), beta = sigmoid,
+    decay = exp(-exp(a_log[h]) softplus(a + dt_bias)).  All outputs float32."""
+    T = proj.shape[0]
+    H, G, D, Dv = num_heads, num_kv_heads, dim, vdim
+    C = 2 * G * D + H * Dv
+    K = taps.shape[1]
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= C + H, "projection rows must hold q, k, v and beta")
+    _need(low.dtype == torch.float32 and low.stride(1) == 1 and low.shape[0] == T and low.shape[1] >= H * D, "low-rank rows must be float32")
+    _f32(taps, "taps", C * K)
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous() and tuple(conv_state.shape[1:]) == (max(K - 1, 0), C),
+          "convolution state must be float32 [slots, K - 1, channels]")
+    _f32(a_log, "A_log", H)
+    _f32(dt_bias, "dt_bias", H * D)
+    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "outputs must be float32 [T, n]")
+    for t, n in ((token_row, "token_row"), (row_q_start, "row_q_start"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("delta_rule")
+    _check(lib.mie_delta_prepare(_ptr(proj), tag(proj), ctypes.c_longlong(proj.stride(0)), _ptr(low), ctypes.c_longlong(low.stride(0)),
+                                 _ptr(taps), _ptr(conv_state), _ptr(token_row), _ptr(row_q_start), _ptr(state_slots), _ptr(a_log),
+                                 _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), T, H, G, D, Dv, K,
+                                 ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), _stream()), "delta_prepare")
+
+
+def conv_state_update(x: torch.Tensor, row_q_start, row_q_len, state_slots, conv_state) -> None:
+    """The last K - 1 inputs ``x`` [T, >= channels] of every row's portion move into its slot of ``conv_state``
+    [slots, K - 1, channels] (older rows of the state shift where the portion is shorter)."""
+    Km1, C = conv_state.shape[1], conv_state.shape[2]
+    _need(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= C, "inputs must hold the channels")
+    _need(conv_state.dtype == torch.float32 and conv_state.is_contiguous(), "convolution state must be contiguous float32")
+    for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("delta_rule")
+    _check(lib.mie_conv_state_update(_ptr(x), tag(x), ctypes.c_longlong(x.stride(0)), _ptr(row_q_start), _ptr(row_q_len),
+                                     _ptr(state_slots), _ptr(conv_state), row_q_len.numel(), C, Km1 + 1, _stream()), "conv_state_update")
+
+
+def delta_scan(qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots, state, out, *, num_heads: int, num_kv_heads: int,
+               dim: int, vdim: int) -> torch.Tensor:
+    """S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q for every new token of every row, from and to
+    ``state`` [slots, H, vdim, dim] float32.  ``out`` [T, H * vdim] float32."""
+    T = qn.shape[0]
+    H, G, D, Dv = num_heads, num_kv_heads, dim, vdim
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, Dv, D), "state must be float32 [slots, H, vdim, dim]")
+    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D), (out, H * Dv)):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "operands must be float32 [T, n]")
+    for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
+        _i32(t, n)
+    lib = load("delta_rule")
+    _check(lib.mie_delta_scan(_ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), _ptr(row_q_start), _ptr(row_q_len),
+                              _ptr(state_slots), _ptr(state), _ptr(out), row_q_len.numel(), H, G, D, Dv, _stream()), "delta_scan")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate, weight, out: torch.Tensor, num_heads: int, vdim: int, eps: float) -> torch.Tensor:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * sigmoid(gate[t, h]) per head of ``vdim`` entries; ``gate`` float32
+    [T, H * vdim], may be a column slice; ``weight`` float32 [vdim]; either may be None."""
+    T = o.shape[0]
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, num_heads * vdim), "o must be float32 [T, H * vdim]")
+    if gate is not None:
+        _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == o.shape, "gate must be float32 [T, H * vdim]")
+    if weight is not None:
+        _f32(weight, "head norm weight", vdim)
+    _need(out.is_contiguous() and out.shape == o.shape, "out must be contiguous [T, H * vdim]")
+    lib = load("delta_rule")
+    _check(lib.mie_head_norm_gate(_ptr(o), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(weight),
+                                  _ptr(out), tag(out), T, num_heads, vdim, ctypes.c_float(eps), _stream()), "head_norm_gate")
+    return out
+
+
+# --------------------------------------------------------------------------- routed experts
+
+EXPERT_ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+
+
+def moe_route(logits: torch.Tensor, top: int):
+    """The ``top`` largest of each row of float32 ``logits`` [T, E] (ties: lower index first) and the softmax over them:
+    (ids int32 [T, top], weights float32 [T, top])."""
+    T, E = logits.shape
+    _f32(logits, "router logits")
+    ids = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    wts = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    lib = load("moe")
+    _check(lib.mie_moe_route(_ptr(logits), _ptr(ids), _ptr(wts), T, E, int(top), _stream()), "moe_route")
+    return ids, wts
+
+
+def moe_dense_act(up: torch.Tensor, ids, wts, act: torch.Tensor, num_experts: int, activation: str) -> torch.Tensor:
+    """act[t, e, :] = weight(t, e) f(up[t, e, :]) for the experts token t chose, 0 for the others (``up`` [T, E * F])."""
+    T = up.shape[0]
+    _need(up.is_contiguous() and act.is_contiguous() and act.shape == up.shape and act.dtype == up.dtype and up.shape[1] % num_experts == 0,
+          "up and act must be contiguous [T, E * F]")
+    lib = load("moe")
+    _check(lib.mie_moe_dense_act(_ptr(up), _ptr(ids), _ptr(wts), _ptr(act), tag(up), T, num_experts, up.shape[1] // num_experts,
+                                 ids.shape[1], EXPERT_ACTIVATIONS[activation], _stream()), "moe_dense_act")
+    return act

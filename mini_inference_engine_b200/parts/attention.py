@@ -178,5 +178,189 @@ class GatedAttention(Mixer):
         return self.rt.linear(gated, self.w_o, None, out_dtype=torch.float32)
 
 
+def _padded_rows(parts, multiple: int = 8):
+    """The matrices of ``parts`` stacked on the output dimension, with zero rows added up to a multiple of ``multiple``
+    (the tensor-core products and 16-byte row accesses want that); returns (matrix, rows before the padding)."""
+    if len({p.dtype for p in parts}) > 1:
+        parts = [p.float() for p in parts]
+    w = torch.cat(parts, 0)
+    n = w.shape[0]
+    if n % multiple:
+        w = torch.cat([w, torch.zeros(multiple - n % multiple, w.shape[1], dtype=w.dtype)], 0)
+    return w, n
+
+
+def _attention_sources(rt, padded: int) -> set:
+    if rt.dtype == torch.float32 or padded > 128:
+        return {"attention_simt"}
+    return {"attention_decode", "attention_prefill_tc" if padded in (64, 128) else "attention_prefill"}
+
+
+class DifferentialAttention(Mixer):
+    """Differential attention: every head has TWO softmax maps (queries and keys twice as wide, laid out head by head
+    as [map 1 | map 2]) over the same values; the head's output is a1 - lambda a2, RMS-normed over its ``vdim`` values (no
+    weight) and scaled by 1 - ``diff``, with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff one number for the layer.
+    Optionally (``gate``) each head is multiplied by sigmoid of one logit per head, 'g' [H, hidden].  No rotation.
+
+    ``shares_kv``: the layer has no key/value projections; it attends over the cache of another layer (the run order
+    names it) with its own queries.
+
+    The two maps are run as 2H query heads over 2G key/value heads by the framework's paged attention kernels: the
+    rows of 'q' are reordered at load time to [group, map, head in group], so that the kernels' rule "query head / (H / G)"
+    finds key head 2g + m, and the rows of 'v' are doubled (each map reads its own copy of the values).  Pages are as wide
+    as the wider of ``dim`` and ``vdim`` (tails zero).  The subtraction, the norm and the gate are one kernel."""
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, diff: float,
+                 eps: float, gate: bool = True, shares_kv: bool = False, window: int | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim = hidden_size, num_heads, num_kv_heads, dim, vdim
+        self.padded = -(-max(dim, vdim) // 16) * 16
+        if self.padded > 256:
+            raise ValueError(f"heads of {max(dim, vdim)}: the attention kernels take up to 256")
+        self.scale, self.diff, self.eps, self.gate, self.shares_kv, self.window = float(scale), float(diff), eps, gate, shares_kv, window
+        self.need = KVNeed(2 * num_kv_heads, self.padded, window)
+
+    def tensor_specs(self):
+        H, G, D, Dv, h = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.hidden_size
+        specs = {"q": TensorSpec((H * 2 * D, h), "fan_in"), "o": TensorSpec((h, H * Dv), "fan_in")}
+        if not self.shares_kv:
+            specs.update({"k": TensorSpec((G * 2 * D, h), "fan_in"), "v": TensorSpec((G * Dv, h), "fan_in")})
+        specs.update({n: TensorSpec((D,), "normal:0:0.3") for n in ("lq1", "lk1", "lq2", "lk2")})
+        if self.gate:
+            specs["g"] = TensorSpec((H, h), "fan_in")
+        return specs
+
+    def bind(self, tensors, rt):
+        import math
+        self.rt = rt
+        H, G, D, Dv, h = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.hidden_size
+        r = H // G
+        # query rows [g, i, m, D] -> [g, m, i, D]
+        q = tensors["q"].reshape(G, r, 2, D, h).permute(0, 2, 1, 3, 4).reshape(H * 2 * D, h)
+        parts = [q]
+        if not self.shares_kv:
+            v = tensors["v"].reshape(G, 1, Dv, h).expand(G, 2, Dv, h).reshape(2 * G * Dv, h)
+            parts += [tensors["k"], v]
+        if self.gate:
+            parts.append(tensors["g"])
+        w, self.rows_used = _padded_rows(parts)
+        self.w_in = rt.place(w)
+        self.w_o = rt.place(tensors["o"])
+        f = lambda n: tensors[n].float()
+        self.lam = float(math.exp(float((f("lq1") * f("lk1")).sum())) - math.exp(float((f("lq2") * f("lk2")).sum())) + self.diff)
+        self.no_freq = torch.zeros(0, dtype=torch.float32, device=rt.device)
+
+    def cache_need(self):
+        return self.need
+
+    def kernel_sources(self):
+        return self.rt.product_sources(self.w_in, self.w_o) | {"qk_norm_rope", "diff_attention"} | _attention_sources(self.rt, self.padded)
+
+    def forward(self, x, ctx, cache):
+        from ..kernels import ops
+        H, G, D, Dv, DP = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.padded
+        T = ctx.num_tokens
+        proj = self.rt.linear(x, self.w_in)
+        q = self.rt.empty(T, 2 * H, DP)
+        writes = cache.writes and not self.shares_kv
+        # (without keys and values of its own the kernel reads the queries only)
+        ops.qk_norm_rope(proj, ctx.positions, ctx.slots[cache.group], self.no_freq, q, cache.k, cache.v, num_heads=2 * H,
+                         num_kv_heads=2 * G, dim=D, vdim=Dv, rot=0, page_size=cache.page_size, write_cache=writes)
+        maps = self.rt.empty(T, 2 * H, DP)
+        attn_kernels.attention(q, ctx, cache, maps, 2 * H, 2 * G, DP, self.scale, self.need.mask(), q_stride=2 * H * DP)
+        gate_at = 2 * H * D + (0 if self.shares_kv else 2 * G * (D + Dv))
+        out = self.rt.empty(T, H * Dv)
+        ops.diff_combine(maps, proj[:, gate_at:gate_at + H] if self.gate else None, out, num_heads=H, group=H // G, vdim=Dv,
+                         lam=self.lam, eps=self.eps, out_scale=1.0 - self.diff)
+        return self.rt.linear(out, self.w_o, None, out_dtype=torch.float32)
+
+
+class LatentAttention(Mixer):
+    """Attention whose queries and keys/values go through low-rank latents.  c_q = RMSnorm(W_dq h) and q = W_uq c_q, per
+    head [``dim`` plain | ``rot_dim`` rotated]; W_dkv h gives the latent c (RMS-normed, ``kv_rank`` entries) and one rotated
+    key part of ``rot_dim`` entries that all heads share; per head the plain key is W_uk c and the value W_uv c.  Rotation
+    pairs entry 2i with 2i + 1 over the first ``rot_dims`` entries of the rotated part.  Causal softmax attention, an
+    output gate sigmoid(W_g h) on the concatenated heads, then W_o.
+
+    The down-projections and the gate are one product; both RMS norms and the rotation of the shared key part one
+    kernel; the up-projections of keys and values one product; queries and keys are put together per head (and keys
+    and values written to the pages) by one more kernel, after which the framework's paged attention kernels run with as
+    many key/value heads as query heads."""
+
+    def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, q_rank: int, kv_rank: int,
+                 scale: float, rot_dims: int, rot_base: float, eps: float, gate: bool = True, window: int | None = None):
+        if rot_dims % 2 or rot_dims > rot_dim:
+            raise ValueError(f"rot_dims {rot_dims} must be even and at most rot_dim {rot_dim}")
+        self.hidden_size, self.num_heads, self.dim, self.rot_dim, self.vdim = hidden_size, num_heads, dim, rot_dim, vdim
+        self.q_rank, self.kv_rank, self.scale, self.eps, self.gate, self.window = q_rank, kv_rank, float(scale), eps, gate, window
+        self.rot_dims, self.rot_base = rot_dims, rot_base
+        self.padded = -(-max(dim + rot_dim, vdim) // 16) * 16
+        if self.padded > 256:
+            raise ValueError(f"heads of {max(dim + rot_dim, vdim)}: the attention kernels take up to 256")
+        self.need = KVNeed(num_heads, self.padded, window)
+
+    def tensor_specs(self):
+        H, D, R, Dv, h = self.num_heads, self.dim, self.rot_dim, self.vdim, self.hidden_size
+        specs = {"dq": TensorSpec((self.q_rank, h), "fan_in"), "dq.norm": TensorSpec((self.q_rank,), "normal:1:0.1"),
+                 "uq": TensorSpec((H * (D + R), self.q_rank), "fan_in"), "dkv": TensorSpec((self.kv_rank + R, h), "fan_in"),
+                 "dkv.norm": TensorSpec((self.kv_rank,), "normal:1:0.1"), "uk": TensorSpec((H * D, self.kv_rank), "fan_in"),
+                 "uv": TensorSpec((H * Dv, self.kv_rank), "fan_in"), "o": TensorSpec((h, H * Dv), "fan_in")}
+        if self.gate:
+            specs["g"] = TensorSpec((H * Dv, h), "fan_in")
+        return specs
+
+    def bind(self, tensors, rt):
+        from .rope import rotary_frequencies
+        self.rt = rt
+        w, _ = _padded_rows([tensors["dq"], tensors["dkv"]] + ([tensors["g"]] if self.gate else []))
+        self.w_down = rt.place(w)
+        self.w_uq = rt.place(tensors["uq"])
+        uk, uv = tensors["uk"], tensors["uv"]
+        if uk.dtype != uv.dtype:
+            uk, uv = uk.float(), uv.float()
+        self.w_ukv = rt.place(torch.cat([uk, uv], 0))
+        self.w_o = rt.place(tensors["o"])
+        small = lambda n: tensors[n].float().to(rt.device).contiguous()
+        self.q_norm, self.c_norm = small("dq.norm"), small("dkv.norm")
+        self.freq = rotary_frequencies(self.rot_dims, self.rot_base).to(rt.device)
+
+    def cache_need(self):
+        return self.need
+
+    def kernel_sources(self):
+        return (self.rt.product_sources(self.w_down, self.w_uq, self.w_ukv, self.w_o) | {"latent_kv", "activation"}
+                | _attention_sources(self.rt, self.padded))
+
+    def forward(self, x, ctx, cache):
+        from ..kernels import ops
+        H, D, R, Dv, DP = self.num_heads, self.dim, self.rot_dim, self.vdim, self.padded
+        T = ctx.num_tokens
+        down = self.rt.linear(x, self.w_down)
+        cq, c = self.rt.empty(T, self.q_rank), self.rt.empty(T, self.kv_rank)
+        kr = self.rt.empty(T, R, dtype=torch.float32)
+        ops.latent_norm_rope(down, ctx.positions, self.freq, self.q_norm, self.c_norm, self.eps, cq, c, kr, q_rank=self.q_rank,
+                             kv_rank=self.kv_rank, rot_dim=R, rot=self.rot_dims)
+        qu = self.rt.linear(cq, self.w_uq)
+        kvu = self.rt.linear(c, self.w_ukv)
+        q = self.rt.empty(T, H, DP)
+        ops.latent_assemble(qu, kvu, kr, ctx.positions, ctx.slots[cache.group], self.freq, q, cache.k, cache.v, num_heads=H, dim=D,
+                            rot_dim=R, vdim=Dv, rot=self.rot_dims, page_size=cache.page_size, write_cache=cache.writes)
+        heads = self.rt.empty(T, H, DP)
+        attn_kernels.attention(q, ctx, cache, heads, H, H, DP, self.scale, self.need.mask(), q_stride=H * DP)
+        if self.gate or DP != Dv:
+            gated = self.rt.empty(T, H * Dv)
+            if self.gate:
+                at = self.q_rank + self.kv_rank + R
+                ops.sigmoid_gate(heads, down[:, at:at + H * Dv], gated, H, Dv)
+            else:
+                gated.view(T, H, Dv).copy_(heads[:, :, :Dv])
+        else:
+            gated = heads.view(T, H * Dv)
+        return self.rt.linear(gated, self.w_o, None, out_dtype=torch.float32)
+
+
 register_part("mixer", "attention", Attention)
 register_part("mixer", "gated_attention", GatedAttention)
+register_part("mixer", "differential_attention", DifferentialAttention)
+register_part("mixer", "latent_attention", LatentAttention)

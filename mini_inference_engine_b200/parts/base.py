@@ -18,6 +18,7 @@ Interfaces (duck-typed; the base classes below only document them and hold the d
   position        rotate_and_store(qkv, ctx, cache, heads, kv_heads)   rotate q (in place) and k, write k, v to the cache
                   project_rotate_and_store(x, w_qkv, b_qkv, ctx, cache, heads, kv_heads) -> qkv   (may fuse the three)
   block           forward(delta, res, ctx, cache) -> delta'            (arrangement of the above)
+  connection      how a sublayer reads from and writes to a stream kept in several copies (coefficients as tensors)
   embedding       forward(ctx) -> res [T, hidden] float32
   head            forward(x[W, hidden]) -> logits [W, vocab] float32
 
@@ -33,7 +34,7 @@ import torch
 from ..config.model_config import PartSpec
 from ..weights.loader import TensorSpec
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "connection")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

@@ -5,6 +5,9 @@ is fused into the *next* norm, so a block takes the pending ``delta`` and return
 add+norm, after the last layer into the final norm)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+
+from ..weights.loader import TensorSpec
 from .base import Part, ResidualSink, StreamValue, register_part
 
 
@@ -102,3 +105,61 @@ class PostNormMixerOnly(PostNormResidual):
 
 register_part("block", "postnorm_residual", PostNormResidual)
 register_part("block", "postnorm_mixer_only", PostNormMixerOnly)
+
+
+class HyperConnection(Part):
+    """How one sublayer is wired to a stream kept in ``streams`` copies x_1 .. x_S: it reads u = sum_s in[s] x_s and,
+    with y its output, writes x_t <- sum_s mix[s, t] x_s + out[t] y into all copies at once (mix is indexed
+    [from, to]).  The coefficients are tensors of the checkpoint: 'in' [S], 'out' [S], 'mix' [S, S]."""
+
+    def __init__(self, streams: int):
+        self.streams = streams
+
+    def tensor_specs(self):
+        S = self.streams
+        return {"in": TensorSpec((S,), f"normal:{1.0 / S}:0.2"), "out": TensorSpec((S,), "normal:1:0.2"),
+                "mix": TensorSpec((S, S), f"normal:{1.0 / S}:0.3")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        small = lambda n: tensors[n].float().reshape(-1).to(rt.device).contiguous()      # read as float32 by the kernel
+        self.in_coef, self.out_coef, self.mix = small("in"), small("out"), small("mix")
+
+
+register_part("connection", "hyper", HyperConnection)
+
+
+@dataclass
+class PendingUpdate:
+    """What a block over a stream in several copies leaves for the next reader of the stream: the output ``y`` of its
+    last sublayer and the ``connection`` that says how it goes into the copies.  The next norm's kernel applies it."""
+    y: object
+    connection: object
+
+
+class HyperConnected(Block):
+    """A pre-norm layer over a stream kept in several copies: each sublayer reads a mixture of the copies through its
+    norm and writes into all of them (``HyperConnection``).  The write of one sublayer and the read and norm of the
+    next are one kernel (the norm's ``read``), so a block takes the pending update of the block before and returns
+    its own; the norm in front of the output head applies the last one."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm",
+             "mixer_connection": "connection", "feed_forward_connection": "connection"}
+
+    def forward(self, delta, res, ctx, cache):
+        if delta is not None and not isinstance(delta, PendingUpdate):
+            raise ValueError("a block over several copies of the stream takes a pending update or nothing")
+        x = self.mixer_norm.read(res, delta, self.mixer_connection)
+        pending = PendingUpdate(self.mixer.forward(x, ctx, cache), self.mixer_connection)
+        if getattr(self, "feed_forward", None) is None:
+            return pending
+        x = self.feed_forward_norm.read(res, pending, self.feed_forward_connection)
+        return PendingUpdate(self.feed_forward.forward(x, ctx), self.feed_forward_connection)
+
+
+class HyperConnectedMixerOnly(HyperConnected):
+    """The same without a feed-forward half."""
+    roles = {"mixer": "mixer", "mixer_norm": "norm", "mixer_connection": "connection"}
+
+
+register_part("block", "hyper_connected", HyperConnected)
+register_part("block", "hyper_connected_mixer_only", HyperConnectedMixerOnly)

@@ -83,3 +83,22 @@ class NormedEmbedding(Embedding):
 
 
 register_part("embedding", "normed_embedding", NormedEmbedding)
+
+
+class ScaledEmbedding(Embedding):
+    """A token embedding times a constant (multiplied in float32), opening a stream kept in ``copies`` copies side by
+    side: [tokens, copies * hidden]."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, copies: int = 1):
+        super().__init__(vocab_size, hidden_size)
+        self.scale, self.copies = float(scale), int(copies)
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.vocab_size, self.hidden_size), "fan_in")}
+
+    def forward(self, ctx):
+        res = self.rt.empty(ctx.num_tokens, self.copies * self.hidden_size, dtype=torch.float32)
+        return ops.embedding(self.weight, ctx.token_ids, res, ctx.token_feedback, scale=self.scale, copies=self.copies)
+
+
+register_part("embedding", "scaled_embedding", ScaledEmbedding)

@@ -101,3 +101,51 @@ class ClampedGLU(FeedForward):
 
 
 register_part("feed_forward", "clamped_glu", ClampedGLU)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of ``num_experts`` small feed-forward layers 'e<i>.up' [ff, hidden], 'e<i>.down' [hidden, ff] without
+    biases, expert(h) = down act(up h).  Router logits 'router' [experts, hidden] are computed in float32; each token
+    uses the ``top`` experts with the largest logits, weighted by the softmax over those logits only.
+
+    All experts' up matrices are stacked into one and their down matrices laid side by side: with the activations of
+    the experts a token did not choose set to zero and those it chose multiplied by their weight, the layer is ONE wide
+    feed-forward, two products of the framework and one kernel between them."""
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, activation: str = "relu2"):
+        if not 1 <= top <= num_experts:
+            raise ValueError(f"top {top} of {num_experts} experts")
+        if activation not in ops.EXPERT_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r}; one of {', '.join(ops.EXPERT_ACTIVATIONS)}")
+        self.hidden_size, self.num_experts, self.top, self.expert_size, self.activation = hidden_size, num_experts, top, expert_size, activation
+
+    def tensor_specs(self):
+        h, F = self.hidden_size, self.expert_size
+        specs = {"router": TensorSpec((self.num_experts, h), "fan_in")}
+        for e in range(self.num_experts):
+            specs[f"e{e}.up"] = TensorSpec((F, h), "fan_in")
+            specs[f"e{e}.down"] = TensorSpec((h, F), "fan_in")
+        return specs
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        ups = [tensors[f"e{e}.up"] for e in range(self.num_experts)]
+        downs = [tensors[f"e{e}.down"] for e in range(self.num_experts)]
+        if len({t.dtype for t in ups + downs}) > 1:
+            ups, downs = [t.float() for t in ups], [t.float() for t in downs]
+        self.w_up = rt.place(torch.cat(ups, 0))                      # [E * F, hidden]
+        self.w_down = rt.place(torch.cat(downs, 1))                  # [hidden, E * F]
+        self.w_router = tensors["router"].float().to(rt.device).contiguous()      # float32: the router's product runs on CUDA cores in 32-bit
+
+    def kernel_sources(self):
+        return {"moe", "gemm_simt"} | self.rt.product_sources(self.w_up, self.w_down)
+
+    def forward(self, x, ctx):
+        logits = self.rt.linear(x, self.w_router, None, out_dtype=torch.float32)
+        ids, wts = ops.moe_route(logits, self.top)
+        up = self.rt.linear(x, self.w_up)
+        act = ops.moe_dense_act(up, ids, wts, torch.empty_like(up), self.num_experts, self.activation)
+        return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -86,3 +86,55 @@ class GroupRMSNorm(Part):
 
 
 register_part("norm", "group_rmsnorm", GroupRMSNorm)
+
+
+class DynamicTanh(Part):
+    """Dynamic Tanh in the place of a norm: tanh(alpha x) * weight + bias per entry, with a learned scalar alpha -- no
+    statistics of the row.  ``streams`` > 1: the stream is kept in that many copies side by side ([tokens, streams *
+    size]); a reader takes one mixture of them and a writer updates all of them (``parts.block.HyperConnection``), and
+    both happen in this norm's kernel, one pass over the stream: ``read`` applies the pending update of the sublayer
+    before (in place), mixes the copies for the reader and squashes.  Called like the other norms
+    (``norm(delta, res, rows)``) it reads the sum of the copies -- the norm in front of the output head; with one copy
+    and a plain tensor as ``delta`` that is the usual fused ``res += delta; x = norm(res)``."""
+
+    def __init__(self, size: int, streams: int = 1):
+        if streams < 1 or streams > 8:
+            raise ValueError(f"{streams} copies of the stream: the kernel takes 1 to 8")
+        self.size, self.streams = size, streams
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.size,), "normal:1:0.1"), "b": TensorSpec((self.size,), "normal:0:0.1"),
+                "alpha": TensorSpec((), "uniform:0.3:1")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        small = lambda n: tensors[n].float().reshape(-1).to(rt.device).contiguous()      # read as float32 by the kernel
+        self.weight, self.bias, self.alpha = small("weight"), small("b"), small("alpha")
+
+    def kernel_sources(self):
+        return {"hyper_norm"}
+
+    def read(self, res, pending=None, reader=None, rows=None):
+        """``pending``: a ``PendingUpdate`` (the output of the sublayer before and its connection) or None; ``reader``:
+        the connection of the sublayer that reads (None: the plain sum of the copies)."""
+        n_out = rows.numel() if rows is not None else res.shape[0]
+        out = self.rt.empty(n_out, self.size)
+        y = conn = None
+        if pending is not None:
+            y, conn = pending.y, pending.connection
+        return ops.hyper_norm(res, self.streams, out, weight=self.weight, bias=self.bias, alpha=self.alpha, y=y,
+                              mix=conn.mix if conn is not None else None, out_coef=conn.out_coef if conn is not None else None,
+                              in_coef=reader.in_coef if reader is not None else None, rows=rows)
+
+    def __call__(self, delta, res, rows=None):
+        from .block import PendingUpdate
+        if isinstance(delta, (StreamValue, StreamUpdated)):
+            delta = None
+        if delta is not None and not isinstance(delta, PendingUpdate):
+            if self.streams != 1:
+                raise ValueError("a stream kept in several copies takes its updates through a connection")
+            delta = PendingUpdate(delta, None)
+        return self.read(res, delta, None, rows)
+
+
+register_part("norm", "dynamic_tanh", DynamicTanh)

@@ -46,6 +46,13 @@ class TensorSpec:
     shape: tuple
     init: str = "normal"      # random-weights mode: "normal" (N(0, 0.02)), "ones", "zeros", "fan_in" (N(0, 1 / last dimension)),
                               # "normal:<mean>:<std>" or "uniform:<low>:<high>"
+    # A dimension of -1 in ``shape`` is read from the checkpoint (a size that config.json does not give, such as the rank of
+    # a low-rank pair); ``default_shape`` is the shape a random model gets then.
+    default_shape: tuple | None = None
+
+    def matches(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == -1 or w == g for w, g in zip(self.shape, shape))
 
 
 def read_model_folder(path: str) -> dict[str, torch.Tensor]:
@@ -76,7 +83,7 @@ def check_and_bind(state: dict[str, torch.Tensor], expected: dict[str, TensorSpe
     unexpected = [n for n in state if n not in in_file
                   and not any(fnmatch.fnmatchcase(n, pat) for pat in ignore)]
     wrong = [(file_name[n], tuple(state[file_name[n]].shape), tuple(s.shape)) for n, s in expected.items()
-             if file_name[n] in state and tuple(state[file_name[n]].shape) != tuple(s.shape)]
+             if file_name[n] in state and not s.matches(state[file_name[n]].shape)]
     if missing or unexpected or wrong:
         raise WeightError(where, sorted(missing), sorted(unexpected), sorted(wrong))
     return {n: state[file_name[n]].to(storage_dtype(state[file_name[n]])) for n in expected}

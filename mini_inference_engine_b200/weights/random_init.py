@@ -25,6 +25,10 @@ def _generator(seed: int, name: str) -> torch.Generator:
 
 
 def random_tensor(seed: int, name: str, spec: TensorSpec, dtype: torch.dtype) -> torch.Tensor:
+    if any(d == -1 for d in spec.shape):
+        if spec.default_shape is None:
+            raise ValueError(f"{name}: a size read from the checkpoint needs a default for a random model")
+        spec = TensorSpec(tuple(spec.default_shape), spec.init)
     if spec.init == "ones":
         return torch.ones(spec.shape, dtype=dtype)
     if spec.init == "zeros":
