@@ -414,9 +414,29 @@ def design_configs(size: dict, vocab=32000, positions=4096):
     return getizen, llama
 
 
+def kebudra_configs(size: dict, vocab=32000, positions=4096):
+    """A Kebudra configuration of the given layer sizes -- latent attention, the gated delta rule and differential attention
+    in turn (the second differential layer reads the first one's keys and values), two copies of the stream, sixteen
+    experts of which a token uses four, sized so that the matrices a token goes through in the feed-forward equal Llama's
+    three -- and the Llama configuration with the same width, heads and number of layers."""
+    from mini_inference_engine_b200.config import load_config
+    w, ff, H, G = size["width"], size["ff"], size["heads"], size["kv_heads"]
+    mlp = dict(kind="moe", expert=dict(ff=(3 * ff // 8 + 63) // 64 * 64), router=dict(experts=16, top=4))
+    lat = dict(type="latent_attention", mlp=mlp, mixer=dict(heads=H, dim=96, rot_dim=32, vdim=128, q_rank=w // 2, kv_rank=w // 4,
+                                                           scale=128 ** -0.5, rot=dict(base=5e5, dims=32)))
+    dlt = dict(type="channel_delta", mlp=mlp, mixer=dict(heads=H, kv_heads=H, dim=128, vdim=128, conv=4, decay_rank=w // 16, gate_rank=w // 16))
+    att = lambda src=None: dict(type="attention", mlp=mlp, mixer=dict(heads=H // 2, kv_heads=max(1, G // 2), dim=128, vdim=128, scale=128 ** -0.5,
+                                                                      diff=0.3, **({} if src is None else {"kv_from": src})))
+    layers = [lat, dlt, att(), lat, att(2), dlt][:size["layers"]]
+    kebudra = load_config(dict(architecture="Kebudra", vocab=vocab, width=w, streams=2, embedding=dict(scale=w ** 0.5), norm=dict(eps=1e-5),
+                               layers=layers))
+    return kebudra, design_configs(size, vocab, positions)[1]
+
+
 KERNEL_FACES = ("embedding", "add_rmsnorm", "stream_norm", "rope_cache_write", "qk_norm_rope", "paged_attention", "prefill_attention",
                 "prefill_attention_tc", "decode_attention", "retention_scan", "head_rms_gate", "causal_conv", "recurrence_gates",
-                "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate")
+                "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate", "hyper_norm", "latent_norm_rope", "latent_assemble",
+                "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_dense_act", "moe_pairs")
 
 
 class KernelTimes:
@@ -464,20 +484,21 @@ class KernelTimes:
 
 
 def run_design(args, steps, warmup):
-    """Prefill and decode throughput of the Getizen design beside Llama at equal layer sizes (random weights), and with
+    """Prefill and decode throughput of the chosen design beside Llama at equal layer sizes (random weights), and with
     ``--kernel-table`` the device time of every kernel of one prompt step and one decode step of both."""
     import torch
 
     from mini_inference_engine_b200 import EngineConfig, LLMEngine
     from mini_inference_engine_b200.weights import write_model_folder
     pk = peaks()
-    out = {"metric": "design_comparison", "design": "Getizen", "beside": "Llama", "dtype": "bf16", "data": "synthetic (random weights, seed 0)",
+    configs_for = {"getizen": design_configs, "kebudra": kebudra_configs}[args.design]
+    out = {"metric": "design_comparison", "design": args.design.capitalize(), "beside": "Llama", "dtype": "bf16", "data": "synthetic (random weights, seed 0)",
            "peaks": pk, "sizes": {}}
     batches = [int(b) for b in args.points.split(",") if b] or [8]
     for size_name in args.sizes.split(","):
         size = DESIGN_SIZES[size_name]
         entry = out["sizes"][size_name] = {"layers": size["layers"]}
-        for label, cfg in zip(("getizen", "llama"), design_configs(size)):
+        for label, cfg in zip((args.design, "llama"), configs_for(size)):
             folder = tempfile.mkdtemp(prefix="mie_b200_bench_")
             try:
                 write_model_folder(folder, cfg, seed=0)
@@ -536,7 +557,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--preset", default="tinyllama-1.1b")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--design", default=None, choices=["getizen"],
+    ap.add_argument("--design", default=None, choices=["getizen", "kebudra"],
                     help="instead of the default workload: prefill and decode throughput of this design beside Llama at equal "
                          "layer sizes (--sizes), random weights; decode batches from --points")
     ap.add_argument("--sizes", default="w2048,w4096", help="with --design: layer sizes to measure, of " + ", ".join(DESIGN_SIZES))

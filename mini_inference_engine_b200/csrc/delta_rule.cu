@@ -10,7 +10,8 @@
 //   conv_state the last K - 1 inputs of the convolution of every row move into its state slot (after prepare has read it);
 //   scan       the recurrence, token by token per row, one block per (row, head, slice of value columns): a group of L
 //              lanes owns one column of S (D / L entries each, in registers), so S is read from memory once per step and
-//              written once.  The read-out uses S after the token's own write:
+//              written once; the tokens' operands arrive through a ring in shared memory filled by asynchronous copies
+//              two batches ahead.  The read-out uses S after the token's own write:
 //              o = (g S)^T q + u (k . q), which needs one pass over the column for both sums.
 //   head_norm_gate   o / rms(o) per head, times a weight shared by the heads, times sigmoid of a gate logit.
 //
@@ -100,17 +101,31 @@ __global__ void conv_state_kernel(const T* __restrict__ x, int64_t stride, const
     }
 }
 
+// Four bytes from global to shared memory without passing through registers; groups of such copies complete in order.
+__device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+#define DELTA_BATCHES 3     // batches of tokens in the shared-memory ring: one computed, two on their way
+
+// The recurrence is one dependent chain per token, so a token's operands must be at hand when its turn comes: the block
+// copies k, q, the decays, beta and its columns of v for `tb` tokens at a time into a ring in shared memory
+// (asynchronous copies, two batches ahead of the one being computed).  ring[slot] = [k: D | q: D | g: D | v: cols | beta].
 __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn,
                                   const float* __restrict__ beta, const float* __restrict__ decay,
                                   const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
                                   const int* __restrict__ state_slots, float* __restrict__ state, float* __restrict__ out, int H,
-                                  int G, int D, int Dv, int L, int cols) {
+                                  int G, int D, int Dv, int L, int cols, int tb) {
+    extern __shared__ __align__(16) float ring[];
     pdl_enter();
     const int row = blockIdx.x, h = blockIdx.y;
-    const int l = threadIdx.x % L, j = blockIdx.z * cols + threadIdx.x / L;
-    const bool active = (int)(threadIdx.x / L) < cols && j < Dv;      // threads that only fill up the last warp own no column
+    const int l = threadIdx.x % L, cl = threadIdx.x / L, j0 = blockIdx.z * cols, j = j0 + cl;
+    const bool active = cl < cols && j < Dv;                   // threads that only fill up the last warp own no column
     const int n = row_q_len[row], t0 = row_q_start[row];
     const int kh = h / (H / G);
+    const int slot_floats = 3 * D + cols + 1;
     float* sp = state + (((int64_t)state_slots[row] * H + h) * Dv + (active ? j : 0)) * D;
     float s[DELTA_R];
 #pragma unroll
@@ -118,47 +133,59 @@ __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __r
         const int i = l + L * r;
         s[r] = (active && i < D) ? sp[i] : 0.f;
     }
-    float nk[DELTA_R], nq[DELTA_R], ng[DELTA_R], nv = 0.f, nb = 0.f;
-    auto fetch = [&](int t) {
-        const float* kp = kn + ((int64_t)t * G + kh) * D;
-        const float* qp = qn + ((int64_t)t * G + kh) * D;
-        const float* gp = decay + ((int64_t)t * H + h) * D;
-#pragma unroll
-        for (int r = 0; r < DELTA_R; ++r) {
-            const int i = l + L * r;
-            const bool ok = i < D;
-            nk[r] = ok ? kp[i] : 0.f;
-            nq[r] = ok ? qp[i] : 0.f;
-            ng[r] = ok ? gp[i] : 0.f;
+    const int batches = (n + tb - 1) / tb;
+    auto issue = [&](int batch) {                              // every thread commits one group per call, also an empty one
+        if (batch < batches) {
+            float* base = ring + (size_t)(batch % DELTA_BATCHES) * tb * slot_floats;
+            const int first = batch * tb, count = min(tb, n - first);
+            for (int idx = threadIdx.x; idx < count * slot_floats; idx += blockDim.x) {
+                const int tok = idx / slot_floats, c = idx - tok * slot_floats;
+                const int64_t t = t0 + first + tok;
+                const float* src;
+                if (c < D) src = kn + (t * G + kh) * D + c;
+                else if (c < 2 * D) src = qn + (t * G + kh) * D + (c - D);
+                else if (c < 3 * D) src = decay + (t * H + h) * D + (c - 2 * D);
+                else if (c < 3 * D + cols) src = vn + (t * H + h) * Dv + min(j0 + (c - 3 * D), Dv - 1);
+                else src = beta + t * H + h;
+                cp_async4(base + idx, src);
+            }
         }
-        nv = active ? vn[((int64_t)t * H + h) * Dv + j] : 0.f;
-        nb = beta[(int64_t)t * H + h];
+        cp_async_commit();
     };
-    if (n > 0) fetch(t0);
-    for (int tok = 0; tok < n; ++tok) {
-        const int t = t0 + tok;
-        float k[DELTA_R], q[DELTA_R];
-        float r1 = 0.f, r2 = 0.f, kq = 0.f;
-        const float v = nv, b = nb;
+    issue(0);
+    issue(1);
+    for (int batch = 0; batch < batches; ++batch) {
+        issue(batch + 2);                                      // into the slot whose batch was computed before the last barrier
+        cp_async_wait_group<2>();                              // this thread's copies of `batch` have landed ...
+        __syncthreads();                                       // ... and everybody else's
+        const float* base = ring + (size_t)(batch % DELTA_BATCHES) * tb * slot_floats;
+        const int first = batch * tb, count = min(tb, n - first);
+        for (int tok = 0; tok < count; ++tok) {
+            const float* op = base + tok * slot_floats;
+            float k[DELTA_R];
+            float r1 = 0.f, r2 = 0.f, kq = 0.f;
 #pragma unroll
-        for (int r = 0; r < DELTA_R; ++r) {
-            k[r] = nk[r];
-            q[r] = nq[r];
-            s[r] *= ng[r];
-            r1 = fmaf(s[r], k[r], r1);
-            r2 = fmaf(s[r], q[r], r2);
-            kq = fmaf(k[r], q[r], kq);
-        }
-        if (tok + 1 < n) fetch(t + 1);              // the next token's operands travel while this one is reduced
-        for (int o = L >> 1; o > 0; o >>= 1) {
-            r1 += __shfl_xor_sync(0xffffffffu, r1, o);
-            r2 += __shfl_xor_sync(0xffffffffu, r2, o);
-            kq += __shfl_xor_sync(0xffffffffu, kq, o);
-        }
-        const float u = b * (v - r1);
+            for (int r = 0; r < DELTA_R; ++r) {
+                const int i = l + L * r;
+                const bool ok = i < D;
+                k[r] = ok ? op[i] : 0.f;
+                const float q = ok ? op[D + i] : 0.f;
+                s[r] *= ok ? op[2 * D + i] : 0.f;
+                r1 = fmaf(s[r], k[r], r1);
+                r2 = fmaf(s[r], q, r2);
+                kq = fmaf(k[r], q, kq);
+            }
+            for (int o = L >> 1; o > 0; o >>= 1) {
+                r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+                kq += __shfl_xor_sync(0xffffffffu, kq, o);
+            }
+            const float u = op[3 * D + cols] * ((cl < cols ? op[3 * D + cl] : 0.f) - r1);
 #pragma unroll
-        for (int r = 0; r < DELTA_R; ++r) s[r] = fmaf(k[r], u, s[r]);
-        if (active && l == 0) out[((int64_t)t * H + h) * Dv + j] = fmaf(u, kq, r2);
+            for (int r = 0; r < DELTA_R; ++r) s[r] = fmaf(k[r], u, s[r]);
+            if (active && l == 0) out[((int64_t)(t0 + first + tok) * H + h) * Dv + j] = fmaf(u, kq, r2);
+        }
+        __syncthreads();                                       // the slot may be refilled
     }
     if (active) {
 #pragma unroll
@@ -240,8 +267,18 @@ extern "C" int mie_delta_scan(const float* qn, const float* kn, const float* vn,
     if (cols > Dv) cols = Dv;
     const int threads = (cols * L + 31) / 32 * 32;
     const dim3 grid(num_rows, H, (Dv + cols - 1) / cols);
-    return launch_kernel(delta_scan_kernel, grid, dim3(threads), 0, stream, qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots,
-                         state, out, H, G, D, Dv, L, cols);
+    // tokens a batch of the ring: eight where three such batches stay within 48 KB, fewer for long keys
+    const size_t slot_bytes = (size_t)(3 * D + cols + 1) * sizeof(float);
+    int tb = (int)(48 * 1024 / (DELTA_BATCHES * slot_bytes));
+    if (tb > 8) tb = 8;
+    if (tb < 1) tb = 1;
+    const size_t smem = (size_t)DELTA_BATCHES * tb * slot_bytes;
+    if (smem > 48 * 1024) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return launch_kernel(delta_scan_kernel, grid, dim3(threads), smem, stream, qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots,
+                         state, out, H, G, D, Dv, L, cols, tb);
 }
 
 extern "C" int mie_head_norm_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out, int tag,

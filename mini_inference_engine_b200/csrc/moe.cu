@@ -7,6 +7,11 @@
 //              experts' matrices stacked): act[t, e, :] = weight(t, e) f(up[t, e, :]) for a chosen expert, 0 for the others,
 //              so that one product with the experts' down matrices side by side gives the weighted sum of the chosen
 //              experts' outputs.  f: 0 relu(x)^2, 1 silu, 2 gelu (tanh form).
+//   pairs_up / pairs_down   the same layer for a handful of tokens (decoding): a (token, chosen expert) pair streams only
+//              its expert's rows -- one warp a matrix row, 16-byte loads -- so a step reads the experts that were chosen
+//              and no others.  up: hid[pair, :] = weight f(W_up[e] x_t); down: out[t, :] = sum_k W_down[e_k] hid[pair_k, :]
+//              (float32, the k in order).  The matrices are the stacked ones of the wide form: W_up [E * F, h] and
+//              W_down [h, E * F].
 #include "common.cuh"
 
 __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int num_tokens, int E,
@@ -59,6 +64,106 @@ __global__ void moe_dense_act_kernel(const T* __restrict__ up, const int* __rest
     }
 }
 
+// Eight consecutive matrix entries as float32 (16 bytes of bfloat16, or two 16-byte loads of float32).
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* v);
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float* v) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// The dot product of a matrix row (n entries, 16-byte aligned, n a multiple of 8) with a float32 vector in shared memory.
+template <typename TW>
+__device__ __forceinline__ float row_dot(const TW* __restrict__ row, const float* __restrict__ x, int n, int lane) {
+    float acc = 0.f;
+    for (int c = lane * 8; c < n; c += 256) {
+        float w[8];
+        load8<TW>(row + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc = fmaf(w[i], x[c + i], acc);
+    }
+    return warp_sum(acc);
+}
+
+#define MOE_ROWS_PER_WARP 4
+
+template <typename TA, typename TW>
+__global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ ids,
+                                    const float* __restrict__ wts, TA* __restrict__ hid, int h, int F, int top, int kind) {
+    extern __shared__ __align__(16) float xs[];               // the token's input, float32
+    pdl_enter();
+    const int pair = blockIdx.x, t = pair / top;
+    const int e = ids[pair];
+    const float weight = wts[pair];
+    for (int c = threadIdx.x; c < h; c += blockDim.x) xs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int f0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
+    for (int f = f0; f < min(f0 + MOE_ROWS_PER_WARP, F); ++f) {
+        const float d = row_dot<TW>(w_up + ((int64_t)e * F + f) * h, xs, h, lane);
+        if (lane == 0) hid[(int64_t)pair * F + f] = from_f32<TA>(weight * expert_act(d, kind));
+    }
+}
+
+template <typename TA, typename TW>
+__global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __restrict__ w_down, const int* __restrict__ ids,
+                                      float* __restrict__ out, int h, int E, int F, int top) {
+    extern __shared__ __align__(16) float hs[];               // the token's `top` hidden rows, float32 [top, F]
+    pdl_enter();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < top * F; c += blockDim.x) hs[c] = to_f32<TA>(hid[(int64_t)t * top * F + c]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int n0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
+    for (int n = n0; n < min(n0 + MOE_ROWS_PER_WARP, h); ++n) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k)
+            acc += row_dot<TW>(w_down + (int64_t)n * E * F + (int64_t)ids[t * top + k] * F, hs + k * F, F, lane);
+        if (lane == 0) out[(int64_t)t * h + n] = acc;
+    }
+}
+
+template <typename TA, typename TW>
+static int launch_pairs(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
+                        int T, int h, int E, int F, int top, int kind, cudaStream_t stream) {
+    const int threads = 256, rows = (threads / 32) * MOE_ROWS_PER_WARP;
+    const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(moe_pairs_down_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    if (e != cudaSuccess) return (int)e;
+    int rc = launch_kernel(moe_pairs_up_kernel<TA, TW>, dim3(T * top, (F + rows - 1) / rows), dim3(threads), smem_up, stream, (const TA*)x,
+                           (const TW*)w_up, ids, wts, (TA*)hid, h, F, top, kind);
+    if (rc != 0) return rc;
+    return launch_kernel(moe_pairs_down_kernel<TA, TW>, dim3(T, (h + rows - 1) / rows), dim3(threads), smem_down, stream, (const TA*)hid,
+                         (const TW*)w_down, ids, out, h, E, F, top);
+}
+
+// Whether the pair kernels take these sizes: rows of whole 16-byte pieces, and a token's hidden rows within shared memory.
+extern "C" int mie_moe_pairs_fit(int h, int F, int top) {
+    return h % 8 == 0 && F % 8 == 0 && (size_t)h * sizeof(float) <= 200 * 1024 && (size_t)top * F * sizeof(float) <= 200 * 1024;
+}
+
+// x [T, h] and hid [T * top, F] in the activation type (act_tag), w_up [E * F, h] and w_down [h, E * F] in w_tag, out [T, h] float32.
+extern "C" int mie_moe_pairs(const void* x, int act_tag, const void* w_up, const void* w_down, int w_tag, const int* ids, const float* wts,
+                             void* hid, float* out, int num_tokens, int h, int E, int F, int top, int kind, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || kind < 0 || kind > 2 || !mie_moe_pairs_fit(h, F, top)) return MIE_ERR_BAD_ARG;
+    if (((reinterpret_cast<uintptr_t>(w_up) | reinterpret_cast<uintptr_t>(w_down)) & 15) != 0) return MIE_ERR_BAD_ARG;
+    if (act_tag == MIE_F32 && w_tag == MIE_F32)
+        return launch_pairs<float, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+    if (act_tag == MIE_BF16 && w_tag == MIE_BF16)
+        return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+    if (act_tag == MIE_BF16 && w_tag == MIE_F32)
+        return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+    return MIE_ERR_BAD_ARG;
+}
+
 extern "C" int mie_moe_route(const float* z, int* ids, float* wts, int num_tokens, int E, int top, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E) return MIE_ERR_BAD_ARG;
@@ -67,12 +172,44 @@ extern "C" int mie_moe_route(const float* z, int* ids, float* wts, int num_token
                          E, top);
 }
 
+// The same, eight bfloat16 a thread; an expert the token did not choose is written as zeros without reading its inputs.
+__global__ void moe_dense_act_bf16x8_kernel(const bf16* __restrict__ up, const int* __restrict__ ids, const float* __restrict__ wts,
+                                            bf16* __restrict__ act, int64_t total8, int E, int F8, int top, int kind) {
+    pdl_enter();
+    const int64_t EF8 = (int64_t)E * F8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / EF8;
+        const int e = (int)((idx - t * EF8) / F8);
+        float w = 0.f;
+        for (int k = 0; k < top; ++k)
+            if (ids[t * top + k] == e) w = wts[t * top + k];
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (w != 0.f) {
+            const uint4 u = *reinterpret_cast<const uint4*>(up + idx * 8);
+            const __nv_bfloat162* hu = reinterpret_cast<const __nv_bfloat162*>(&u);
+            __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(hu[i]);
+                ho[i] = __floats2bfloat162_rn(w * expert_act(f.x, kind), w * expert_act(f.y, kind));
+            }
+        }
+        *reinterpret_cast<uint4*>(act + idx * 8) = o;
+    }
+}
+
 extern "C" int mie_moe_dense_act(const void* up, const int* ids, const float* wts, void* act, int tag, int num_tokens, int E, int F,
                                  int top, int kind, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (E <= 0 || F <= 0 || top <= 0 || kind < 0 || kind > 2) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)num_tokens * E * F;
     const int threads = 256;
+    if (tag == MIE_BF16 && F % 8 == 0 && ((reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(act)) & 15) == 0) {
+        int64_t blocks8 = (total / 8 + threads - 1) / threads;
+        if (blocks8 > (int64_t)device_sm_count() * 16) blocks8 = (int64_t)device_sm_count() * 16;
+        return launch_kernel(moe_dense_act_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)up, ids, wts,
+                             (bf16*)act, total / 8, E, F / 8, top, kind);
+    }
     int64_t blocks = (total + threads - 1) / threads;
     if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
     if (tag == MIE_F32)

@@ -950,3 +950,29 @@ def moe_dense_act(up: torch.Tensor, ids, wts, act: torch.Tensor, num_experts: in
     _check(lib.mie_moe_dense_act(_ptr(up), _ptr(ids), _ptr(wts), _ptr(act), tag(up), T, num_experts, up.shape[1] // num_experts,
                                  ids.shape[1], EXPERT_ACTIVATIONS[activation], _stream()), "moe_dense_act")
     return act
+
+
+def moe_pairs_fit(hidden: int, expert_size: int, top: int) -> bool:
+    """Whether ``moe_pairs`` takes these sizes (rows of whole 16-byte pieces; a token's hidden rows in shared memory)."""
+    return bool(load("moe").mie_moe_pairs_fit(int(hidden), int(expert_size), int(top)))
+
+
+def moe_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids, wts, out: torch.Tensor, num_experts: int,
+              activation: str) -> torch.Tensor:
+    """The routed experts for a handful of tokens: every (token, chosen expert) pair reads its expert's rows of the
+    stacked matrices ``w_up`` [E * F, h] and ``w_down`` [h, E * F] and nothing else.  out [T, h] float32 = sum over the
+    token's pairs of weight * W_down[e] f(W_up[e] x)."""
+    T, h = x.shape
+    top = ids.shape[1]
+    EF = w_up.shape[0]
+    F = EF // num_experts
+    _need(x.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_up.shape == (EF, h) and w_down.shape == (h, EF)
+          and w_up.dtype == w_down.dtype and F * num_experts == EF, "stacked expert matrices must be contiguous [E * F, h] and [h, E * F]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, h), "out must be float32 [T, h]")
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == ids.shape,
+          "ids int32 and weights float32 [T, top]")
+    hid = torch.empty(T * top, F, dtype=x.dtype, device=x.device)
+    lib = load("moe")
+    _check(lib.mie_moe_pairs(_ptr(x), tag(x), _ptr(w_up), _ptr(w_down), tag(w_up), _ptr(ids), _ptr(wts), _ptr(hid), _ptr(out), T, h,
+                             int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], _stream()), "moe_pairs")
+    return out

@@ -226,7 +226,7 @@ class DifferentialAttention(Mixer):
         specs = {"q": TensorSpec((H * 2 * D, h), "fan_in"), "o": TensorSpec((h, H * Dv), "fan_in")}
         if not self.shares_kv:
             specs.update({"k": TensorSpec((G * 2 * D, h), "fan_in"), "v": TensorSpec((G * Dv, h), "fan_in")})
-        specs.update({n: TensorSpec((D,), "normal:0:0.3") for n in ("lq1", "lk1", "lq2", "lk2")})
+        specs.update({n: TensorSpec((D,), "normal:0:0.1") for n in ("lq1", "lk1", "lq2", "lk2")})
         if self.gate:
             specs["g"] = TensorSpec((H, h), "fan_in")
         return specs

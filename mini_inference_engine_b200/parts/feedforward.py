@@ -108,9 +108,11 @@ class RoutedExperts(FeedForward):
     biases, expert(h) = down act(up h).  Router logits 'router' [experts, hidden] are computed in float32; each token
     uses the ``top`` experts with the largest logits, weighted by the softmax over those logits only.
 
-    All experts' up matrices are stacked into one and their down matrices laid side by side: with the activations of
-    the experts a token did not choose set to zero and those it chose multiplied by their weight, the layer is ONE wide
-    feed-forward, two products of the framework and one kernel between them."""
+    All experts' up matrices are stacked into one and their down matrices laid side by side.  Many tokens (prompt
+    portions, large batches): with the activations of the experts a token did not choose set to zero and those it chose
+    multiplied by their weight, the layer is ONE wide feed-forward -- two products of the framework on the tensor cores
+    and one kernel between them.  A handful of tokens (no more (token, expert) pairs than experts): every pair streams
+    its own expert's rows and no others, so a decoding step reads only the experts that were chosen."""
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, activation: str = "relu2"):
         if not 1 <= top <= num_experts:
@@ -143,6 +145,11 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         logits = self.rt.linear(x, self.w_router, None, out_dtype=torch.float32)
         ids, wts = ops.moe_route(logits, self.top)
+        T = x.shape[0]
+        if (T * self.top <= self.num_experts and x.is_contiguous() and (x.dtype == self.w_up.dtype or self.w_up.dtype == torch.float32)
+                and ops.moe_pairs_fit(self.hidden_size, self.expert_size, self.top)):
+            out = torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device)
+            return ops.moe_pairs(x, self.w_up, self.w_down, ids, wts, out, self.num_experts, self.activation)
         up = self.rt.linear(x, self.w_up)
         act = ops.moe_dense_act(up, ids, wts, torch.empty_like(up), self.num_experts, self.activation)
         return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)

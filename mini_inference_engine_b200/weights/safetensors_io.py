@@ -79,7 +79,7 @@ def write_file(path: str, tensors: dict[str, torch.Tensor], metadata: dict | Non
         t = tensors[name].detach().contiguous().cpu()
         if t.dtype not in _NAMES:
             raise SafetensorsError(f"cannot store dtype {t.dtype} (tensor {name!r})")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # (a scalar is flattened first)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
