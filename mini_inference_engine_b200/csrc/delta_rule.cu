@@ -9,7 +9,7 @@
 //              sigmoid of its logit, g = exp(-exp(A_log[h]) softplus(a + dt_bias)) -- all float32;
 //   conv_state the last K - 1 inputs of the convolution of every row move into its state slot (after prepare has read it);
 //   scan       the recurrence, token by token per row, one block per (row, head, slice of value columns): a group of L
-//              lanes owns one column of S (D / L entries each, in registers), so S is read from memory once per step and
+//              lanes owns one column of S (D / L entries each, in registers: 4, 8 or 16 by the key size), so S is read from memory once per step and
 //              written once; the tokens' operands arrive through a ring in shared memory filled by asynchronous copies
 //              two batches ahead.  The read-out uses S after the token's own write:
 //              o = (g S)^T q + u (k . q), which needs one pass over the column for both sums.
@@ -19,7 +19,7 @@
 // input at K - 1 - i tokens before the next one.  Slot 0 is scratch.
 #include "common.cuh"
 
-#define DELTA_R 16          // entries of a column a lane holds
+#define DELTA_MAX_KEY 512    // the longest key: sixteen entries a lane, thirty-two lanes a column
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -45,8 +45,8 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int64_t stride,
                                      const int* __restrict__ token_row, const int* __restrict__ row_q_start,
                                      const int* __restrict__ state_slots, const float* __restrict__ a_log,
                                      const float* __restrict__ dt_bias, float* __restrict__ qn, float* __restrict__ kn,
-                                     float* __restrict__ vn, float* __restrict__ beta, float* __restrict__ decay, int H, int G,
-                                     int D, int Dv, int K, float q_scale, float unit_eps) {
+                                     float* __restrict__ vn, float* __restrict__ beta, float* __restrict__ decay,
+                                     float* __restrict__ kq, int H, int G, int D, int Dv, int K, float q_scale, float unit_eps) {
     pdl_enter();
     const int t = blockIdx.x;
     const int row = token_row[t];
@@ -79,6 +79,13 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int64_t stride,
         const float rate = expf(a_log[i / D]);
         decay[(int64_t)t * H * D + i] = expf(-rate * softplus_f(low[(int64_t)t * low_stride + i] + dt_bias[i]));
     }
+    __syncthreads();                                   // q and k of this token, written above by other warps of the block
+    for (int g = warp; g < G; g += nw) {               // k . q per key head: the same for every value column of the recurrence
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(qn[((int64_t)t * G + g) * D + d], kn[((int64_t)t * G + g) * D + d], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) kq[(int64_t)t * G + g] = acc;
+    }
 }
 
 // The convolution state of every row after the step: row i of the new state is the input at q_len - (K - 1) + i of the
@@ -108,16 +115,24 @@ __device__ __forceinline__ void cp_async4(float* dst_smem, const float* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+__device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
+}
+
 #define DELTA_BATCHES 3     // batches of tokens in the shared-memory ring: one computed, two on their way
 
 // The recurrence is one dependent chain per token, so a token's operands must be at hand when its turn comes: the block
-// copies k, q, the decays, beta and its columns of v for `tb` tokens at a time into a ring in shared memory
-// (asynchronous copies, two batches ahead of the one being computed).  ring[slot] = [k: D | q: D | g: D | v: cols | beta].
+// copies k, q, the decays, its columns of v, beta and k . q for `tb` tokens at a time into a ring in shared memory
+// (asynchronous copies, two batches ahead of the one being computed).  ring[slot] = [k: D | q: D | g: D | v: cols | beta | kq],
+// padded to whole 16-byte pieces.  A lane holds R entries of its column: few, so that a column's sums are spread
+// over many lanes and an SM holds many warps whose chains hide one another's latency.  VEC: D = L * R and D % 4 = 0, so the
+// ring is filled and read 16 bytes at a time and nothing needs a bound check; otherwise everything goes entry by entry.
+template <int R, bool VEC>
 __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn,
-                                  const float* __restrict__ beta, const float* __restrict__ decay,
+                                  const float* __restrict__ beta, const float* __restrict__ decay, const float* __restrict__ kq,
                                   const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
                                   const int* __restrict__ state_slots, float* __restrict__ state, float* __restrict__ out, int H,
-                                  int G, int D, int Dv, int L, int cols, int tb) {
+                                  int G, int D, int Dv, int L, int cols, int tb, int slot_floats) {
     extern __shared__ __align__(16) float ring[];
     pdl_enter();
     const int row = blockIdx.x, h = blockIdx.y;
@@ -125,29 +140,45 @@ __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __r
     const bool active = cl < cols && j < Dv;                   // threads that only fill up the last warp own no column
     const int n = row_q_len[row], t0 = row_q_start[row];
     const int kh = h / (H / G);
-    const int slot_floats = 3 * D + cols + 1;
     float* sp = state + (((int64_t)state_slots[row] * H + h) * Dv + (active ? j : 0)) * D;
-    float s[DELTA_R];
+    // register r of lane l holds row 4 (l + L (r / 4)) + r % 4: pieces of four consecutive rows, dealt out over the lanes,
+    // so that the lanes of a column read consecutive 16-byte pieces of the ring (no bank conflicts)
+    auto row_of = [&](int r) { return 4 * (l + L * (r >> 2)) + (r & 3); };
+    float s[R];
 #pragma unroll
-    for (int r = 0; r < DELTA_R; ++r) {
-        const int i = l + L * r;
+    for (int r = 0; r < R; ++r) {
+        const int i = row_of(r);
         s[r] = (active && i < D) ? sp[i] : 0.f;
     }
+    const int v_at = 3 * D + (cl < cols ? cl : 0);
+    const float v_on = cl < cols ? 1.f : 0.f;
     const int batches = (n + tb - 1) / tb;
     auto issue = [&](int batch) {                              // every thread commits one group per call, also an empty one
         if (batch < batches) {
             float* base = ring + (size_t)(batch % DELTA_BATCHES) * tb * slot_floats;
             const int first = batch * tb, count = min(tb, n - first);
-            for (int idx = threadIdx.x; idx < count * slot_floats; idx += blockDim.x) {
-                const int tok = idx / slot_floats, c = idx - tok * slot_floats;
-                const int64_t t = t0 + first + tok;
-                const float* src;
-                if (c < D) src = kn + (t * G + kh) * D + c;
-                else if (c < 2 * D) src = qn + (t * G + kh) * D + (c - D);
-                else if (c < 3 * D) src = decay + (t * H + h) * D + (c - 2 * D);
-                else if (c < 3 * D + cols) src = vn + (t * H + h) * Dv + min(j0 + (c - 3 * D), Dv - 1);
-                else src = beta + t * H + h;
-                cp_async4(base + idx, src);
+            const int64_t tf = t0 + first;
+            if constexpr (VEC) {
+                const int q4 = D >> 2;                         // 16-byte pieces of one operand
+                for (int c = threadIdx.x; c < 3 * q4; c += blockDim.x) {
+                    const int seg = c / q4, off = (c - seg * q4) * 4;
+                    const float* src = seg == 0 ? kn + (tf * G + kh) * D : (seg == 1 ? qn + (tf * G + kh) * D : decay + (tf * H + h) * D);
+                    const int64_t step = seg < 2 ? (int64_t)G * D : (int64_t)H * D;
+                    float* dst = base + seg * D + off;
+                    for (int tok = 0; tok < count; ++tok) cp_async16(dst + tok * slot_floats, src + off + tok * step);
+                }
+            } else {
+                for (int c = threadIdx.x; c < 3 * D; c += blockDim.x) {
+                    const int seg = c / D, off = c - seg * D;
+                    const float* src = seg == 0 ? kn + (tf * G + kh) * D : (seg == 1 ? qn + (tf * G + kh) * D : decay + (tf * H + h) * D);
+                    const int64_t step = seg < 2 ? (int64_t)G * D : (int64_t)H * D;
+                    for (int tok = 0; tok < count; ++tok) cp_async4(base + tok * slot_floats + c, src + off + tok * step);
+                }
+            }
+            for (int c = threadIdx.x; c < cols + 2; c += blockDim.x) {
+                const float* src = c < cols ? vn + (tf * H + h) * Dv + min(j0 + c, Dv - 1) : (c == cols ? beta + tf * H + h : kq + tf * G + kh);
+                const int64_t step = c < cols ? (int64_t)H * Dv : (c == cols ? H : G);
+                for (int tok = 0; tok < count; ++tok) cp_async4(base + tok * slot_floats + 3 * D + c, src + tok * step);
             }
         }
         cp_async_commit();
@@ -162,35 +193,52 @@ __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __r
         const int first = batch * tb, count = min(tb, n - first);
         for (int tok = 0; tok < count; ++tok) {
             const float* op = base + tok * slot_floats;
-            float k[DELTA_R];
-            float r1 = 0.f, r2 = 0.f, kq = 0.f;
+            float k[R], q[R], g[R];
+            if constexpr (VEC) {
 #pragma unroll
-            for (int r = 0; r < DELTA_R; ++r) {
-                const int i = l + L * r;
-                const bool ok = i < D;
-                k[r] = ok ? op[i] : 0.f;
-                const float q = ok ? op[D + i] : 0.f;
-                s[r] *= ok ? op[2 * D + i] : 0.f;
-                r1 = fmaf(s[r], k[r], r1);
-                r2 = fmaf(s[r], q, r2);
-                kq = fmaf(k[r], q, kq);
+                for (int r = 0; r < R; r += 4) {
+                    const int i = 4 * (l + L * (r >> 2));
+                    *reinterpret_cast<float4*>(k + r) = *reinterpret_cast<const float4*>(op + i);
+                    *reinterpret_cast<float4*>(q + r) = *reinterpret_cast<const float4*>(op + D + i);
+                    *reinterpret_cast<float4*>(g + r) = *reinterpret_cast<const float4*>(op + 2 * D + i);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int i = row_of(r);
+                    const bool ok = i < D;
+                    k[r] = ok ? op[i] : 0.f;
+                    q[r] = ok ? op[D + i] : 0.f;
+                    g[r] = ok ? op[2 * D + i] : 0.f;
+                }
             }
+            float r1 = 0.f, r2 = 0.f, r1b = 0.f, r2b = 0.f;             // two chains each: half the dependent latency
+#pragma unroll
+            for (int r = 0; r < R; r += 2) {
+                s[r] *= g[r];
+                s[r + 1] *= g[r + 1];
+                r1 = fmaf(s[r], k[r], r1);
+                r1b = fmaf(s[r + 1], k[r + 1], r1b);
+                r2 = fmaf(s[r], q[r], r2);
+                r2b = fmaf(s[r + 1], q[r + 1], r2b);
+            }
+            r1 += r1b;
+            r2 += r2b;
             for (int o = L >> 1; o > 0; o >>= 1) {
                 r1 += __shfl_xor_sync(0xffffffffu, r1, o);
                 r2 += __shfl_xor_sync(0xffffffffu, r2, o);
-                kq += __shfl_xor_sync(0xffffffffu, kq, o);
             }
-            const float u = op[3 * D + cols] * ((cl < cols ? op[3 * D + cl] : 0.f) - r1);
+            const float u = op[3 * D + cols] * (v_on * op[v_at] - r1);
 #pragma unroll
-            for (int r = 0; r < DELTA_R; ++r) s[r] = fmaf(k[r], u, s[r]);
-            if (active && l == 0) out[((int64_t)(t0 + first + tok) * H + h) * Dv + j] = fmaf(u, kq, r2);
+            for (int r = 0; r < R; ++r) s[r] = fmaf(k[r], u, s[r]);
+            if (active && l == 0) out[((int64_t)(t0 + first + tok) * H + h) * Dv + j] = fmaf(u, op[3 * D + cols + 1], r2);
         }
         __syncthreads();                                       // the slot may be refilled
     }
     if (active) {
 #pragma unroll
-        for (int r = 0; r < DELTA_R; ++r) {
-            const int i = l + L * r;
+        for (int r = 0; r < R; ++r) {
+            const int i = row_of(r);
             if (i < D) sp[i] = s[r];
         }
     }
@@ -223,7 +271,7 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
 extern "C" int mie_delta_prepare(const void* proj, int tag, long long stride, const float* low, long long low_stride, const float* taps,
                                  const float* conv_state, const int* token_row, const int* row_q_start, const int* state_slots,
                                  const float* a_log, const float* dt_bias, float* qn, float* kn, float* vn, float* beta, float* decay,
-                                 int num_tokens, int H, int G, int D, int Dv, int K, float q_scale, float unit_eps,
+                                 float* kq, int num_tokens, int H, int G, int D, int Dv, int K, float q_scale, float unit_eps,
                                  cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0 || K < 1) return MIE_ERR_BAD_ARG;
@@ -232,11 +280,11 @@ extern "C" int mie_delta_prepare(const void* proj, int tag, long long stride, co
     if (tag == MIE_F32)
         return launch_kernel(delta_prepare_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)proj, (int64_t)stride,
                              low, (int64_t)low_stride, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias, qn, kn, vn,
-                             beta, decay, H, G, D, Dv, K, q_scale, unit_eps);
+                             beta, decay, kq, H, G, D, Dv, K, q_scale, unit_eps);
     else if (tag == MIE_BF16)
         return launch_kernel(delta_prepare_kernel<bf16>, dim3(num_tokens), dim3(threads), 0, stream, (const bf16*)proj, (int64_t)stride,
                              low, (int64_t)low_stride, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias, qn, kn, vn,
-                             beta, decay, H, G, D, Dv, K, q_scale, unit_eps);
+                             beta, decay, kq, H, G, D, Dv, K, q_scale, unit_eps);
     return MIE_ERR_BAD_ARG;
 }
 
@@ -255,30 +303,45 @@ extern "C" int mie_conv_state_update(const void* x, int tag, long long stride, c
     return MIE_ERR_BAD_ARG;
 }
 
-extern "C" int mie_delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay,
-                              const int* row_q_start, const int* row_q_len, const int* state_slots, float* state, float* out,
-                              int num_rows, int H, int G, int D, int Dv, cudaStream_t stream) {
-    if (num_rows <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0) return MIE_ERR_BAD_ARG;
+template <int R>
+static int launch_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const float* kq,
+                       const int* row_q_start, const int* row_q_len, const int* state_slots, float* state, float* out, int num_rows,
+                       int H, int G, int D, int Dv, cudaStream_t stream) {
     int L = 1;
-    while (L * DELTA_R < D) L <<= 1;
-    if (L > 32) return MIE_ERR_TOO_LARGE;                      // key sizes beyond 32 x DELTA_R
+    while (L * R < D) L <<= 1;
+    if (L > 32) return MIE_ERR_TOO_LARGE;
     int cols = 128 / L;                                        // value columns a block of 128 threads
     if (cols > Dv) cols = Dv;
     const int threads = (cols * L + 31) / 32 * 32;
     const dim3 grid(num_rows, H, (Dv + cols - 1) / cols);
     // tokens a batch of the ring: eight where three such batches stay within 48 KB, fewer for long keys
-    const size_t slot_bytes = (size_t)(3 * D + cols + 1) * sizeof(float);
+    const int slot_floats = (3 * D + cols + 2 + 3) / 4 * 4;
+    const size_t slot_bytes = (size_t)slot_floats * sizeof(float);
     int tb = (int)(48 * 1024 / (DELTA_BATCHES * slot_bytes));
     if (tb > 8) tb = 8;
     if (tb < 1) tb = 1;
     const size_t smem = (size_t)DELTA_BATCHES * tb * slot_bytes;
+    const bool vec = D == L * R && D % 4 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(decay)) & 15) == 0;
+    auto kernel = vec ? delta_scan_kernel<R, true> : delta_scan_kernel<R, false>;
     if (smem > 48 * 1024) {
-        const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    return launch_kernel(delta_scan_kernel, grid, dim3(threads), smem, stream, qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots,
-                         state, out, H, G, D, Dv, L, cols, tb);
+    return launch_kernel(kernel, grid, dim3(threads), smem, stream, qn, kn, vn, beta, decay, kq, row_q_start, row_q_len,
+                         state_slots, state, out, H, G, D, Dv, L, cols, tb, slot_floats);
+}
+
+extern "C" int mie_delta_scan(const float* qn, const float* kn, const float* vn, const float* beta, const float* decay, const float* kq,
+                              const int* row_q_start, const int* row_q_len, const int* state_slots, float* state, float* out,
+                              int num_rows, int H, int G, int D, int Dv, cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || D <= 0 || Dv <= 0) return MIE_ERR_BAD_ARG;
+    // entries of a column a lane: the fewest for which sixteen lanes hold a column (thirty-two for the longest keys)
+    if (D <= 64) return launch_scan<4>(qn, kn, vn, beta, decay, kq, row_q_start, row_q_len, state_slots, state, out, num_rows, H, G, D, Dv, stream);
+    if (D <= 128) return launch_scan<8>(qn, kn, vn, beta, decay, kq, row_q_start, row_q_len, state_slots, state, out, num_rows, H, G, D, Dv, stream);
+    if (D <= DELTA_MAX_KEY) return launch_scan<16>(qn, kn, vn, beta, decay, kq, row_q_start, row_q_len, state_slots, state, out, num_rows, H, G, D, Dv, stream);
+    return MIE_ERR_TOO_LARGE;
 }
 
 extern "C" int mie_head_norm_gate(const float* o, const float* gate, long long gate_stride, const float* w, void* out, int tag,

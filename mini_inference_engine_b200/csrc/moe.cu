@@ -12,6 +12,10 @@
 //              and no others.  up: hid[pair, :] = weight f(W_up[e] x_t); down: out[t, :] = sum_k W_down[e_k] hid[pair_k, :]
 //              (float32, the k in order).  The matrices are the stacked ones of the wide form: W_up [E * F, h] and
 //              W_down [h, E * F].
+//   sort / gather / act_rows / combine   the same layer for many tokens with the products done expert by expert (a grouped
+//              product over rows sorted by expert): sort gives every (token, expert) pair its place among its expert's
+//              rows and the experts' row ranges; gather copies the tokens' inputs to those places; act_rows applies
+//              weight f(.) row by row; combine adds a token's rows up in float32, the pairs in order.
 #include "common.cuh"
 
 __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int num_tokens, int E,
@@ -161,6 +165,140 @@ extern "C" int mie_moe_pairs(const void* x, int act_tag, const void* w_up, const
         return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
     if (act_tag == MIE_BF16 && w_tag == MIE_F32)
         return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+    return MIE_ERR_BAD_ARG;
+}
+
+#define MOE_SORT_MAX_EXPERTS 1024
+
+// One block.  ends[e] = one past the last sorted row of expert e (the running sum of the experts' pair counts);
+// place[p] = the sorted row of pair p = (token p / top, choice p % top); row_weight[place[p]] = wts[p].  Which of an
+// expert's rows a pair gets depends on the order the threads arrive in; no result depends on it, since every row is
+// computed by itself and read back through place[].
+__global__ void moe_sort_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int* __restrict__ ends,
+                                int* __restrict__ place, float* __restrict__ row_weight, int pairs, int E) {
+    __shared__ int count[MOE_SORT_MAX_EXPERTS];
+    __shared__ int start[MOE_SORT_MAX_EXPERTS];
+    pdl_enter();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[min(max(ids[p], 0), E - 1)], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { start[e] = run; run += count[e]; ends[e] = run; }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int at = atomicAdd(&start[min(max(ids[p], 0), E - 1)], 1);
+        place[p] = at;
+        row_weight[at] = wts[p];
+    }
+}
+
+// rows[place[p]] = x[p / top] for every pair p; 16 bytes a thread where rows allow it.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ place, T* __restrict__ rows, int pairs, int h,
+                                  int top, int vec) {
+    pdl_enter();
+    const int per = 16 / (int)sizeof(T);
+    const int n = vec ? h / per : h;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (int64_t)pairs * n; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int p = (int)(idx / n), c = (int)(idx - (int64_t)p * n);
+        const T* src = x + (int64_t)(p / top) * h;
+        T* dst = rows + (int64_t)place[p] * h;
+        if (vec) reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+        else dst[c] = src[c];
+    }
+}
+
+// up[r, :] <- row_weight[r] f(up[r, :]) in place.
+template <typename T>
+__global__ void moe_act_rows_kernel(T* __restrict__ up, const float* __restrict__ row_weight, int64_t total, int F, int kind) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x)
+        up[idx] = from_f32<T>(row_weight[idx / F] * expert_act(to_f32<T>(up[idx]), kind));
+}
+__global__ void moe_act_rows_bf16x8_kernel(bf16* __restrict__ up, const float* __restrict__ row_weight, int64_t total8, int F8, int kind) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const float w = row_weight[idx / F8];
+        uint4 u = *reinterpret_cast<const uint4*>(up + idx * 8);
+        __nv_bfloat162* hu = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(hu[i]);
+            hu[i] = __floats2bfloat162_rn(w * expert_act(f.x, kind), w * expert_act(f.y, kind));
+        }
+        *reinterpret_cast<uint4*>(up + idx * 8) = u;
+    }
+}
+
+// out[t, :] = sum over k < top of rows[place[t * top + k], :], float32, k in order.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ place, float* __restrict__ out, int num_tokens,
+                                   int h, int top) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (int64_t)num_tokens * h; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / h), c = (int)(idx - (int64_t)t * h);
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc += to_f32<T>(rows[(int64_t)place[t * top + k] * h + c]);
+        out[idx] = acc;
+    }
+}
+
+static int capped_blocks(int64_t items, int threads) {
+    int64_t blocks = (items + threads - 1) / threads;
+    if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
+    return (int)(blocks < 1 ? 1 : blocks);
+}
+
+extern "C" int mie_moe_sort(const int* ids, const float* wts, int* ends, int* place, float* row_weight, int pairs, int E,
+                            cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (E <= 0) return MIE_ERR_BAD_ARG;
+    if (E > MOE_SORT_MAX_EXPERTS) return MIE_ERR_TOO_LARGE;
+    return launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, ids, wts, ends, place, row_weight, pairs, E);
+}
+
+extern "C" int mie_moe_gather(const void* x, const int* place, void* rows, int tag, int pairs, int h, int top, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (h <= 0 || top <= 0) return MIE_ERR_BAD_ARG;
+    const int el = tag == MIE_F32 ? 4 : 2;
+    const int vec = (h * el) % 16 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(rows)) & 15) == 0;
+    const int64_t items = (int64_t)pairs * (vec ? h * el / 16 : h);
+    if (tag == MIE_F32)
+        return launch_kernel(moe_gather_kernel<float>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const float*)x, place,
+                             (float*)rows, pairs, h, top, vec);
+    else if (tag == MIE_BF16)
+        return launch_kernel(moe_gather_kernel<bf16>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const bf16*)x, place,
+                             (bf16*)rows, pairs, h, top, vec);
+    return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_moe_act_rows(void* up, const float* row_weight, int tag, int rows, int F, int kind, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (F <= 0 || kind < 0 || kind > 2) return MIE_ERR_BAD_ARG;
+    const int64_t total = (int64_t)rows * F;
+    if (tag == MIE_BF16 && F % 8 == 0 && (reinterpret_cast<uintptr_t>(up) & 15) == 0)
+        return launch_kernel(moe_act_rows_bf16x8_kernel, dim3(capped_blocks(total / 8, 256)), dim3(256), 0, stream, (bf16*)up, row_weight,
+                             total / 8, F / 8, kind);
+    if (tag == MIE_F32)
+        return launch_kernel(moe_act_rows_kernel<float>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (float*)up, row_weight, total, F, kind);
+    else if (tag == MIE_BF16)
+        return launch_kernel(moe_act_rows_kernel<bf16>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (bf16*)up, row_weight, total, F, kind);
+    return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, int tag, int num_tokens, int h, int top, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (h <= 0 || top <= 0) return MIE_ERR_BAD_ARG;
+    const int64_t items = (int64_t)num_tokens * h;
+    if (tag == MIE_F32)
+        return launch_kernel(moe_combine_kernel<float>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const float*)rows, place, out,
+                             num_tokens, h, top);
+    else if (tag == MIE_BF16)
+        return launch_kernel(moe_combine_kernel<bf16>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const bf16*)rows, place, out,
+                             num_tokens, h, top);
     return MIE_ERR_BAD_ARG;
 }
 

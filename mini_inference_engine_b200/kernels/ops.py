@@ -851,11 +851,11 @@ def diff_combine(maps: torch.Tensor, gate, out: torch.Tensor, *, num_heads: int,
 # --------------------------------------------------------------------------- gated delta rule
 
 def delta_prepare(proj: torch.Tensor, low: torch.Tensor, taps, conv_state, token_row, row_q_start, state_slots, a_log, dt_bias,
-                  qn, kn, vn, beta, decay, *, num_heads: int, num_kv_heads: int, dim: int, vdim: int, unit_eps: float) -> None:
+                  qn, kn, vn, beta, decay, kq, *, num_heads: int, num_kv_heads: int, dim: int, vdim: int, unit_eps: float) -> None:
     """From rows [q: G x dim | k: G x dim | v: H x vdim | beta logits: H | ...] of the input projection and float32 rows
     [a: H x dim | ...] of the low-rank one: convolution over time + silu of q, k, v (float32 taps [channels, K], older inputs
     from ``conv_state`` [slots, K - 1, channels]), q and k unit vectors per head (q times dim^-1/2), beta = sigmoid,
-    decay = exp(-exp(a_log[h]) softplus(a + dt_bias)).  All outputs float32."""
+    decay = exp(-exp(a_log[h]) softplus(a + dt_bias)), kq = k . q per key head.  All outputs float32."""
     T = proj.shape[0]
     H, G, D, Dv = num_heads, num_kv_heads, dim, vdim
     C = 2 * G * D + H * Dv
@@ -867,14 +867,14 @@ def delta_prepare(proj: torch.Tensor, low: torch.Tensor, taps, conv_state, token
           "convolution state must be float32 [slots, K - 1, channels]")
     _f32(a_log, "A_log", H)
     _f32(dt_bias, "dt_bias", H * D)
-    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D)):
+    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D), (kq, G)):
         _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "outputs must be float32 [T, n]")
     for t, n in ((token_row, "token_row"), (row_q_start, "row_q_start"), (state_slots, "state_slots")):
         _i32(t, n)
     lib = load("delta_rule")
     _check(lib.mie_delta_prepare(_ptr(proj), tag(proj), ctypes.c_longlong(proj.stride(0)), _ptr(low), ctypes.c_longlong(low.stride(0)),
                                  _ptr(taps), _ptr(conv_state), _ptr(token_row), _ptr(row_q_start), _ptr(state_slots), _ptr(a_log),
-                                 _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), T, H, G, D, Dv, K,
+                                 _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), _ptr(kq), T, H, G, D, Dv, K,
                                  ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), _stream()), "delta_prepare")
 
 
@@ -891,19 +891,19 @@ def conv_state_update(x: torch.Tensor, row_q_start, row_q_len, state_slots, conv
                                      _ptr(state_slots), _ptr(conv_state), row_q_len.numel(), C, Km1 + 1, _stream()), "conv_state_update")
 
 
-def delta_scan(qn, kn, vn, beta, decay, row_q_start, row_q_len, state_slots, state, out, *, num_heads: int, num_kv_heads: int,
+def delta_scan(qn, kn, vn, beta, decay, kq, row_q_start, row_q_len, state_slots, state, out, *, num_heads: int, num_kv_heads: int,
                dim: int, vdim: int) -> torch.Tensor:
     """S <- decay S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q for every new token of every row, from and to
     ``state`` [slots, H, vdim, dim] float32.  ``out`` [T, H * vdim] float32."""
     T = qn.shape[0]
     H, G, D, Dv = num_heads, num_kv_heads, dim, vdim
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, Dv, D), "state must be float32 [slots, H, vdim, dim]")
-    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D), (out, H * Dv)):
+    for t, n in ((qn, G * D), (kn, G * D), (vn, H * Dv), (beta, H), (decay, H * D), (kq, G), (out, H * Dv)):
         _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape == (T, n), "operands must be float32 [T, n]")
     for t, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
         _i32(t, n)
     lib = load("delta_rule")
-    _check(lib.mie_delta_scan(_ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), _ptr(row_q_start), _ptr(row_q_len),
+    _check(lib.mie_delta_scan(_ptr(qn), _ptr(kn), _ptr(vn), _ptr(beta), _ptr(decay), _ptr(kq), _ptr(row_q_start), _ptr(row_q_len),
                               _ptr(state_slots), _ptr(state), _ptr(out), row_q_len.numel(), H, G, D, Dv, _stream()), "delta_scan")
     return out
 
@@ -976,3 +976,53 @@ def moe_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids, wt
     _check(lib.mie_moe_pairs(_ptr(x), tag(x), _ptr(w_up), _ptr(w_down), tag(w_up), _ptr(ids), _ptr(wts), _ptr(hid), _ptr(out), T, h,
                              int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], _stream()), "moe_pairs")
     return out
+
+
+def moe_sort(ids: torch.Tensor, wts: torch.Tensor, num_experts: int):
+    """Places for the (token, expert) pairs of ``ids`` [T, top] among rows sorted by expert: (ends int32 [E], one past each
+    expert's last row; place int32 [T * top], the row of every pair; row_weight float32 [T * top], the pairs' weights by row)."""
+    pairs = ids.numel()
+    _need(ids.dtype == torch.int32 and ids.is_contiguous() and wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == ids.shape,
+          "ids int32 and weights float32 [T, top]")
+    ends = torch.empty(num_experts, dtype=torch.int32, device=ids.device)
+    place = torch.empty(pairs, dtype=torch.int32, device=ids.device)
+    row_weight = torch.empty(pairs, dtype=torch.float32, device=ids.device)
+    _check(load("moe").mie_moe_sort(_ptr(ids), _ptr(wts), _ptr(ends), _ptr(place), _ptr(row_weight), pairs, int(num_experts), _stream()),
+           "moe_sort")
+    return ends, place, row_weight
+
+
+def moe_gather(x: torch.Tensor, place: torch.Tensor, top: int) -> torch.Tensor:
+    """rows[place[p]] = x[p // top]: the tokens' inputs where their pairs' rows are."""
+    T, h = x.shape
+    _need(x.is_contiguous() and place.numel() == T * top, "x must be contiguous [T, h] with top places a token")
+    rows = torch.empty(T * top, h, dtype=x.dtype, device=x.device)
+    _check(load("moe").mie_moe_gather(_ptr(x), _ptr(place), _ptr(rows), tag(x), T * top, h, int(top), _stream()), "moe_gather")
+    return rows
+
+
+def moe_act_rows(up: torch.Tensor, row_weight: torch.Tensor, activation: str) -> torch.Tensor:
+    """up[r] <- row_weight[r] f(up[r]) in place."""
+    _need(up.is_contiguous() and row_weight.numel() == up.shape[0] and row_weight.dtype == torch.float32, "one float32 weight a row")
+    _check(load("moe").mie_moe_act_rows(_ptr(up), _ptr(row_weight), tag(up), up.shape[0], up.shape[1], EXPERT_ACTIVATIONS[activation],
+                                        _stream()), "moe_act_rows")
+    return up
+
+
+def moe_combine(rows: torch.Tensor, place: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over k of rows[place[t * top + k]], float32."""
+    T, h = out.shape
+    _need(rows.is_contiguous() and rows.shape == (T * top, h) and out.dtype == torch.float32 and out.is_contiguous(), "rows [T * top, h], out float32 [T, h]")
+    _check(load("moe").mie_moe_combine(_ptr(rows), _ptr(place), _ptr(out), tag(rows), T, h, int(top), _stream()), "moe_combine")
+    return out
+
+
+def grouped_linear(rows: torch.Tensor, b: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:
+    """The product of row ranges with a matrix each: rows [R, K] bfloat16 sorted by group, b [groups, K, N] (any strides
+    with one unit stride per matrix), ends int32 [groups] one past each group's last row -> [R, N] bfloat16.  The library's
+    grouped product (float32 accumulation), as the plain products of prompt-sized steps are the library's."""
+    _need(rows.is_cuda and rows.dtype == torch.bfloat16 == b.dtype and rows.is_contiguous() and ends.dtype == torch.int32,
+          "grouped product: bfloat16 rows and matrices on the device, int32 ends")
+    global launches
+    launches += 1
+    return torch._grouped_mm(rows, b, offs=ends)

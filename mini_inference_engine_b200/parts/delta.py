@@ -84,13 +84,13 @@ class ChannelDelta(Mixer):
         proj = self.rt.linear(x, self.w_in)
         low = self.rt.linear(self.rt.linear(x, self.w_low), self.w_up, None, out_dtype=torch.float32)     # [a: H x D | gate: H x Dv]
         f32 = lambda n: self.rt.empty(T, n, dtype=torch.float32)
-        qn, kn, vn, beta, decay = f32(G * D), f32(G * D), f32(H * Dv), f32(H), f32(H * D)
+        qn, kn, vn, beta, decay, kq = f32(G * D), f32(G * D), f32(H * Dv), f32(H), f32(H * D), f32(G)
         ops.delta_prepare(proj, low, self.conv, conv_state, ctx.token_row, ctx.row_q_start, ctx.state_slots, self.a_log, self.dt_bias,
-                          qn, kn, vn, beta, decay, num_heads=H, num_kv_heads=G, dim=D, vdim=Dv, unit_eps=self.unit_eps)
+                          qn, kn, vn, beta, decay, kq, num_heads=H, num_kv_heads=G, dim=D, vdim=Dv, unit_eps=self.unit_eps)
         if self.taps > 1:
             ops.conv_state_update(proj, ctx.row_q_start, ctx.row_q_len, ctx.state_slots, conv_state)
         o = f32(H * Dv)
-        ops.delta_scan(qn, kn, vn, beta, decay, ctx.row_q_start, ctx.row_q_len, ctx.state_slots, state, o, num_heads=H,
+        ops.delta_scan(qn, kn, vn, beta, decay, kq, ctx.row_q_start, ctx.row_q_len, ctx.state_slots, state, o, num_heads=H,
                        num_kv_heads=G, dim=D, vdim=Dv)
         gated = self.rt.empty(T, H * Dv)
         ops.head_norm_gate(o, low[:, H * D:], self.norm, gated, H, Dv, self.eps)

@@ -103,6 +103,9 @@ class ClampedGLU(FeedForward):
 register_part("feed_forward", "clamped_glu", ClampedGLU)
 
 
+GROUPED_MIN_TOKENS = 32      # = kernels.linear.AUTO_MAX_TOKENS: above it the plain products are the library's too
+
+
 class RoutedExperts(FeedForward):
     """A mixture of ``num_experts`` small feed-forward layers 'e<i>.up' [ff, hidden], 'e<i>.down' [hidden, ff] without
     biases, expert(h) = down act(up h).  Router logits 'router' [experts, hidden] are computed in float32; each token
@@ -112,7 +115,9 @@ class RoutedExperts(FeedForward):
     portions, large batches): with the activations of the experts a token did not choose set to zero and those it chose
     multiplied by their weight, the layer is ONE wide feed-forward -- two products of the framework on the tensor cores
     and one kernel between them.  A handful of tokens (no more (token, expert) pairs than experts): every pair streams
-    its own expert's rows and no others, so a decoding step reads only the experts that were chosen."""
+    its own expert's rows and no others, so a decoding step reads only the experts that were chosen.  Many tokens in
+    bfloat16 where a token uses at most half of the experts: the pairs are sorted by expert and both products run expert
+    by expert over those rows (the library's grouped product), so no expert computes for a token that did not choose it."""
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, activation: str = "relu2"):
         if not 1 <= top <= num_experts:
@@ -138,6 +143,12 @@ class RoutedExperts(FeedForward):
         self.w_up = rt.place(torch.cat(ups, 0))                      # [E * F, hidden]
         self.w_down = rt.place(torch.cat(downs, 1))                  # [hidden, E * F]
         self.w_router = tensors["router"].float().to(rt.device).contiguous()      # float32: the router's product runs on CUDA cores in 32-bit
+        E, F, h = self.num_experts, self.expert_size, self.hidden_size
+        self.grouped = (rt.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and 2 * self.top <= E and h % 8 == 0 and F % 8 == 0
+                        and hasattr(torch, "_grouped_mm") and rt.device.type == "cuda")
+        if self.grouped:       # views of the stacked matrices, one [K, N] operand per expert; nothing is copied
+            self.b_up = self.w_up.view(E, F, h).transpose(1, 2)
+            self.b_down = torch.as_strided(self.w_down, (E, F, h), (F, 1, E * F))
 
     def kernel_sources(self):
         return {"moe", "gemm_simt"} | self.rt.product_sources(self.w_up, self.w_down)
@@ -150,6 +161,14 @@ class RoutedExperts(FeedForward):
                 and ops.moe_pairs_fit(self.hidden_size, self.expert_size, self.top)):
             out = torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device)
             return ops.moe_pairs(x, self.w_up, self.w_down, ids, wts, out, self.num_experts, self.activation)
+        # up to the token count that the framework's own streaming product serves, the wide form reads every expert once at
+        # that kernel's rate, which the grouped product does not reach on so few rows
+        if self.grouped and x.dtype == torch.bfloat16 and x.is_contiguous() and T > GROUPED_MIN_TOKENS:
+            ends, place, row_weight = ops.moe_sort(ids, wts, self.num_experts)
+            rows = ops.moe_gather(x, place, self.top)
+            hid = ops.moe_act_rows(ops.grouped_linear(rows, self.b_up, ends), row_weight, self.activation)
+            down = ops.grouped_linear(hid, self.b_down, ends)
+            return ops.moe_combine(down, place, self.top, torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device))
         up = self.rt.linear(x, self.w_up)
         act = ops.moe_dense_act(up, ids, wts, torch.empty_like(up), self.num_experts, self.activation)
         return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)

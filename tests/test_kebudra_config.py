@@ -83,3 +83,28 @@ def test_refused_configurations(change, word):
     change(c)
     with pytest.raises(ConfigError, match=word):
         load_config(c)
+
+
+def test_preset_and_the_benchmark_pair_of_equal_size():
+    """The shipped tiny preset reads back, and bench.py's --design option builds a Kebudra and a Llama configuration of the
+    same width, heads and number of layers, the feed-forward matrices a token goes through as large as Llama's three."""
+    import importlib.util
+    import os
+
+    from mini_inference_engine_b200.config import load_preset, preset_names
+    assert "tiny-kebudra" in preset_names()
+    cfg = load_preset("tiny-kebudra")
+    assert [l["type"] for l in cfg.layers] == ["latent_attention", "channel_delta", "attention", "attention"] and cfg.streams == 2
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for size in bench.DESIGN_SIZES.values():
+        k, l = bench.kebudra_configs(size)
+        assert k.width == l.hidden_size == size["width"] and len(k.layers) == l.num_hidden_layers == size["layers"]
+        assert {x["type"] for x in k.layers} == {"latent_attention", "channel_delta", "attention"}
+        mlp = k.layers[0]["mlp"]
+        used = mlp["router"]["top"] * mlp["expert"]["ff"] * 2
+        assert abs(used - 3 * l.intermediate_size) <= 0.05 * 3 * l.intermediate_size
+        lat = next(x for x in k.layers if x["type"] == "latent_attention")["mixer"]
+        assert lat["heads"] == l.num_attention_heads and lat["dim"] + lat["rot_dim"] == l.head_dim

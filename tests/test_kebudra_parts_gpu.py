@@ -270,7 +270,7 @@ def test_delta_rule_state_holds_a_far_token_and_long_decoding(dt):
 # ----------------------------------------------------------------------------------------------- routed experts
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("experts,top,ff", [(6, 2, 24), (5, 1, 10), (3, 3, 16), (1, 1, 8), (17, 4, 33)])
+@pytest.mark.parametrize("experts,top,ff", [(6, 2, 24), (5, 1, 10), (3, 3, 16), (1, 1, 8), (17, 4, 33), (40, 2, 16)])
 def test_routed_experts(dt, experts, top, ff):
     from mini_inference_engine_b200.parts import StepContext  # noqa: F401  (the part takes the step's context and ignores it)
     rt = rt_for(dt)
