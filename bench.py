@@ -436,7 +436,7 @@ def kebudra_configs(size: dict, vocab=32000, positions=4096):
 KERNEL_FACES = ("embedding", "add_rmsnorm", "stream_norm", "rope_cache_write", "qk_norm_rope", "paged_attention", "prefill_attention",
                 "prefill_attention_tc", "decode_attention", "retention_scan", "head_rms_gate", "causal_conv", "recurrence_gates",
                 "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate", "hyper_norm", "latent_norm_rope", "latent_assemble",
-                "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_dense_act", "moe_pairs", "moe_sort", "moe_gather", "moe_act_rows", "moe_combine", "grouped_linear")
+                "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_router", "moe_dense_act", "moe_pairs", "moe_sort", "moe_gather", "moe_act_rows", "moe_combine", "grouped_linear")
 
 
 class KernelTimes:

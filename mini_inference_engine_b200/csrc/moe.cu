@@ -1,6 +1,8 @@
 // A routed mixture of experts: the router's choice, and the experts' activation for the form in which all experts are
 // one wide feed-forward.
 //
+//   router     route with the logits computed in the same kernel: z = W_router x in float32 (float32 weights, the token's
+//              input widened), a block per token, a warp per expert in turn.
 //   route      per token, from float32 router logits z [T, E]: the `top` experts with the largest logits (ties: the lower
 //              index first), weights = softmax over the chosen logits only.  ids [T, top] int32, wts [T, top] float32.
 //   dense_act  with up[t] = [expert 0: F | expert 1: F | ...] the up-projections of ALL experts (one product with the
@@ -18,12 +20,8 @@
 //              weight f(.) row by row; combine adds a token's rows up in float32, the pairs in order.
 #include "common.cuh"
 
-__global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int num_tokens, int E,
-                                 int top) {
-    pdl_enter();
-    const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= num_tokens) return;
-    const float* zt = z + (int64_t)t * E;
+// The `top` largest of zt[0 .. E) in order (ties: the lower index first) and the softmax over them.
+__device__ __forceinline__ void route_one(const float* zt, int* ids, float* wts, int E, int top) {
     float prev_v = INFINITY;
     int prev_i = -1;
     float first = 0.f, sum = 0.f;
@@ -38,13 +36,53 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ 
         if (bi < 0) { bi = 0; best = -INFINITY; }              // logits that are not numbers: keep the ids in range
         if (k == 0) first = best;
         const float p = expf(best - first);
-        ids[(int64_t)t * top + k] = bi;
-        wts[(int64_t)t * top + k] = p;
+        ids[k] = bi;
+        wts[k] = p;
         sum += p;
         prev_v = best;
         prev_i = bi;
     }
-    for (int k = 0; k < top; ++k) wts[(int64_t)t * top + k] /= sum;
+    for (int k = 0; k < top; ++k) wts[k] /= sum;
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int num_tokens, int E,
+                                 int top) {
+    pdl_enter();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= num_tokens) return;
+    route_one(z + (int64_t)t * E, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top);
+}
+
+// A block per token: x[t] into shared memory as float32, a warp per expert in turn for the logit, then one thread chooses.
+// `logits` (optional) receives z.
+template <typename TA>
+__global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
+                                  float* __restrict__ logits, int h, int E, int top) {
+    extern __shared__ __align__(16) float rs[];               // x [h], then z [E]
+    float* z = rs + h;
+    pdl_enter();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < h; c += blockDim.x) rs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < E; e += nw) {
+        const float* row = w + (int64_t)e * h;
+        float acc = 0.f;
+        if ((h & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+            for (int c = lane * 4; c < h; c += 128) {
+                const float4 a = *reinterpret_cast<const float4*>(row + c), b = *reinterpret_cast<const float4*>(rs + c);
+                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+            }
+        } else {
+            for (int c = lane; c < h; c += 32) acc = fmaf(row[c], rs[c], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (logits)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) logits[(int64_t)t * E + e] = z[e];
+    if (threadIdx.x == 0) route_one(z, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top);
 }
 
 __device__ __forceinline__ float expert_act(float x, int kind) {
@@ -299,6 +337,24 @@ extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, i
     else if (tag == MIE_BF16)
         return launch_kernel(moe_combine_kernel<bf16>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const bf16*)rows, place, out,
                              num_tokens, h, top);
+    return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_moe_router(const void* x, int tag, const float* w, int* ids, float* wts, float* logits, int num_tokens, int h, int E,
+                              int top, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (E <= 0 || top <= 0 || top > E || h <= 0) return MIE_ERR_BAD_ARG;
+    const size_t smem = (size_t)(h + E) * sizeof(float);
+    if (smem > 200 * 1024) return MIE_ERR_TOO_LARGE;
+    const int threads = 256;
+    cudaError_t e;
+    if (tag == MIE_F32) {
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+        return launch_kernel(moe_router_kernel<float>, dim3(num_tokens), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, h, E, top);
+    } else if (tag == MIE_BF16) {
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+        return launch_kernel(moe_router_kernel<bf16>, dim3(num_tokens), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, h, E, top);
+    }
     return MIE_ERR_BAD_ARG;
 }
 

@@ -941,6 +941,22 @@ def moe_route(logits: torch.Tensor, top: int):
     return ids, wts
 
 
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int, logits: torch.Tensor | None = None):
+    """Router logits z = x w_router^T in float32 (``w_router`` float32 [E, h]; ``x`` widened) and the choice of ``moe_route`` in
+    one kernel: (ids int32 [T, top], weights float32 [T, top]); ``logits`` float32 [T, E], if given, receives z."""
+    T, h = x.shape
+    E = w_router.shape[0]
+    _need(x.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape == (E, h),
+          "router: contiguous x [T, h] and float32 weights [E, h]")
+    if logits is not None:
+        _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, E), "logits must be float32 [T, E]")
+    ids = torch.empty(T, top, dtype=torch.int32, device=x.device)
+    wts = torch.empty(T, top, dtype=torch.float32, device=x.device)
+    _check(load("moe").mie_moe_router(_ptr(x), tag(x), _ptr(w_router), _ptr(ids), _ptr(wts), _ptr(logits), T, h, E, int(top), _stream()),
+           "moe_router")
+    return ids, wts
+
+
 def moe_dense_act(up: torch.Tensor, ids, wts, act: torch.Tensor, num_experts: int, activation: str) -> torch.Tensor:
     """act[t, e, :] = weight(t, e) f(up[t, e, :]) for the experts token t chose, 0 for the others (``up`` [T, E * F])."""
     T = up.shape[0]

@@ -151,11 +151,13 @@ class RoutedExperts(FeedForward):
             self.b_down = torch.as_strided(self.w_down, (E, F, h), (F, 1, E * F))
 
     def kernel_sources(self):
-        return {"moe", "gemm_simt"} | self.rt.product_sources(self.w_up, self.w_down)
+        return {"moe", "gemm_simt"} | self.rt.product_sources(self.w_up, self.w_down)       # (gemm_simt: the router of a very wide model)
 
     def forward(self, x, ctx):
-        logits = self.rt.linear(x, self.w_router, None, out_dtype=torch.float32)
-        ids, wts = ops.moe_route(logits, self.top)
+        if x.is_contiguous() and (self.hidden_size + self.num_experts) * 4 <= 200 * 1024:
+            ids, wts = ops.moe_router(x, self.w_router, self.top)          # logits, top-k and weights in one kernel
+        else:
+            ids, wts = ops.moe_route(self.rt.linear(x, self.w_router, None, out_dtype=torch.float32), self.top)
         T = x.shape[0]
         if (T * self.top <= self.num_experts and x.is_contiguous() and (x.dtype == self.w_up.dtype or self.w_up.dtype == torch.float32)
                 and ops.moe_pairs_fit(self.hidden_size, self.expert_size, self.top)):

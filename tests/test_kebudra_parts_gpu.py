@@ -294,3 +294,14 @@ def test_router_takes_the_largest_logits_and_weighs_by_their_softmax():
         want = torch.softmax(z[r].cpu()[ids[r].cpu().long()], 0)
         assert torch.allclose(w[r].cpu(), want, atol=1e-6)
     assert math.isclose(float(w.sum()), 2.0, rel_tol=1e-6)
+    # the same choice with the logits computed in the kernel, from float32 and from bfloat16 inputs
+    g = torch.Generator().manual_seed(3)
+    wr = torch.randn(11, 70, generator=g).to(DEV)
+    for dt in DTYPES:
+        x = torch.randn(9, 70, generator=g).to(dt).to(DEV)
+        logits = torch.empty(9, 11, device=DEV)
+        ids2, w2 = ops.moe_router(x, wr, 4, logits)
+        want = x.float() @ wr.t()
+        assert torch.allclose(logits, want, atol=1e-4, rtol=1e-5)
+        ids3, w3 = ops.moe_route(want.contiguous(), 4)
+        assert torch.equal(ids2, ids3) and torch.allclose(w2, w3, atol=1e-5)
