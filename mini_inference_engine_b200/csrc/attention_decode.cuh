@@ -18,6 +18,7 @@ struct DecodeParams {
     const int* block_tables; int table_stride;
     const int* row_q_start; const int* row_q_len; const int* row_ctx_len;
     bf16* out;
+    float* out32;            // not null: the output goes here as float32 instead (a caller that subtracts attention outputs)
     float* part_o; float* part_lse; int* counters;      // scratch (splits > 1)
     int num_heads, num_kv_heads, page_size, page_shift, window, splits, chunks;
     int stages;              // tiles in flight per block (2, 3 or 4)
@@ -431,10 +432,14 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         const int head = kvh * G + g0 + g;
         if (eff == 1) {
-            uint2 packed;
-            packed.x = pack_bf16(val.x, val.y);
-            packed.y = pack_bf16(val.z, val.w);
-            *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d) = packed;
+            if (p.out32) {
+                *reinterpret_cast<float4*>(p.out32 + ((int64_t)token * p.num_heads + head) * D + d) = val;
+            } else {
+                uint2 packed;
+                packed.x = pack_bf16(val.x, val.y);
+                packed.y = pack_bf16(val.z, val.w);
+                *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d) = packed;
+            }
         } else if (p.cluster) {
             const int owner = idx & (S - 1), li = idx >> (31 - __clz(S));            // S is 2, 4 or 8
             st_cluster_f32x4(cluster_addr(recv_o_addr, owner) + (uint32_t)(split * items_per_owner + li) * 16u, val.x, val.y, val.z, val.w);
@@ -468,10 +473,15 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             }
             const float inv = wsum > 0.f ? __frcp_rn(wsum) : 0.f;
             const int head = kvh * G + g0 + g;
-            uint2 packed;
-            packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
-            packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
-            *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d4) = packed;
+            if (p.out32) {
+                *reinterpret_cast<float4*>(p.out32 + ((int64_t)token * p.num_heads + head) * D + d4) =
+                    make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+            } else {
+                uint2 packed;
+                packed.x = pack_bf16(acc[0] * inv, acc[1] * inv);
+                packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+                *reinterpret_cast<uint2*>(p.out + ((int64_t)token * p.num_heads + head) * D + d4) = packed;
+            }
         }
         return;                                                    // nobody reads this block's memory any more
     }
@@ -501,7 +511,8 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             acc += w * __ldcg(p.part_o + (base + s2) * D + d);
             wsum += w;
         }
-        p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
+        if (p.out32) p.out32[((int64_t)token * p.num_heads + head) * D + d] = wsum > 0.f ? acc / wsum : 0.f;
+        else p.out[((int64_t)token * p.num_heads + head) * D + d] = __float2bfloat16_rn(wsum > 0.f ? acc / wsum : 0.f);
     }
 }
 
@@ -565,7 +576,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
                                    cudaStream_t stream, int stages = 0, int64_t num_pages = 0,
                                    int64_t check_pages = 0, int* report = nullptr, int min_part_tiles = 0,
-                                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0) {
+                                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, bool out_f32 = false) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -579,7 +590,7 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
     p.block_tables = block_tables; p.table_stride = table_stride;
     p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len;
-    p.out = (bf16*)out; p.part_o = part_o; p.part_lse = part_lse; p.counters = counters;
+    p.out = (bf16*)out; p.out32 = out_f32 ? (float*)out : nullptr; p.part_o = part_o; p.part_lse = part_lse; p.counters = counters;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;

@@ -27,6 +27,7 @@ struct PrefillParams {
     const int* block_tables; int table_stride;
     const int* row_q_start; const int* row_q_len; const int* row_ctx_len; int num_rows;
     bf16* out;
+    float* out32;      // not null: the output goes here as float32 instead
     int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
     float scale_log2e;
     int64_t check_pages;     // pages in each cache, for the range check of block-table entries
@@ -218,7 +219,14 @@ prefill_attention_kernel(const PrefillParams p) {
         const int r = wq + quad + h * 8;
         if (r >= nq) continue;
         const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
-        bf16* op = p.out + ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
+        const int64_t at = ((int64_t)(q_start + q0 + r) * p.num_heads + head) * D;
+        if (p.out32) {
+#pragma unroll
+            for (int n = 0; n < NBLK; ++n)
+                *reinterpret_cast<float2*>(p.out32 + at + n * 8 + tq * 2) = make_float2(o[n][h * 2] * inv, o[n][h * 2 + 1] * inv);
+            continue;
+        }
+        bf16* op = p.out + at;
 #pragma unroll
         for (int n = 0; n < NBLK; ++n) {
             *reinterpret_cast<unsigned*>(op + n * 8 + tq * 2) = pack_bf16(o[n][h * 2] * inv, o[n][h * 2 + 1] * inv);
@@ -243,7 +251,7 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
                                      const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens,
                                      void* out, int num_heads, int num_kv_heads, int head_dim, int page_size,
                                      float scale, int window, int min_q_len, long long num_pages, int work_rows,
-                                     int work_tokens, cudaStream_t stream) {
+                                     int work_tokens, int out_f32, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim < 16 || head_dim > PRE_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
@@ -255,6 +263,7 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
     p.block_tables = block_tables; p.table_stride = table_stride;
     p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.num_rows = num_rows;
     p.out = (bf16*)out;
+    p.out32 = out_f32 ? (float*)out : nullptr;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;

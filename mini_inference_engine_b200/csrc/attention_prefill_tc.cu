@@ -43,6 +43,7 @@ struct FaParams {
     const int* block_tables; int table_stride;
     const int* row_q_start; const int* row_q_len; const int* row_ctx_len; int num_rows;
     bf16* out;
+    float* out32;      // not null: the output goes here as float32 instead
     int* error;
     int num_heads, num_kv_heads, page_size, page_shift, window, min_q_len;
     int pair;                // 1: a block takes two query tiles of a row (see the kernel), 0: one
@@ -469,6 +470,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
                         w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
                         w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
+                        if (p.out32) {
+                            float* o32 = p.out32 + (op - p.out) + c;
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4)
+                                *reinterpret_cast<float4*>(o32 + i) = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+                            continue;
+                        }
                         *reinterpret_cast<uint4*>(op + c) = w0;
                         *reinterpret_cast<uint4*>(op + c + 8) = w1;
                     }
@@ -844,6 +852,13 @@ prefill_attention_pp_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         w0.z = pack2_bf16(v[4] * inv, v[5] * inv); w0.w = pack2_bf16(v[6] * inv, v[7] * inv);
                         w1.x = pack2_bf16(v[8] * inv, v[9] * inv); w1.y = pack2_bf16(v[10] * inv, v[11] * inv);
                         w1.z = pack2_bf16(v[12] * inv, v[13] * inv); w1.w = pack2_bf16(v[14] * inv, v[15] * inv);
+                        if (p.out32) {
+                            float* o32 = p.out32 + (op - p.out) + c;
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4)
+                                *reinterpret_cast<float4*>(o32 + i) = make_float4(v[i] * inv, v[i + 1] * inv, v[i + 2] * inv, v[i + 3] * inv);
+                            continue;
+                        }
                         *reinterpret_cast<uint4*>(op + c) = w0;
                         *reinterpret_cast<uint4*>(op + c + 8) = w1;
                     }
@@ -915,7 +930,7 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
                                         int64_t num_pages, const int* block_tables, int table_stride, const int* row_q_start,
                                         const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens, void* out,
                                         int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
-                                        int min_q_len, int work_rows, int work_tokens, cudaStream_t stream) {
+                                        int min_q_len, int work_rows, int work_tokens, int out_f32, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim != 64 && head_dim != 128) return MIE_ERR_BAD_ARG;
@@ -928,7 +943,7 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     FaParams p;
     p.block_tables = block_tables; p.table_stride = table_stride;
     p.row_q_start = row_q_start; p.row_q_len = row_q_len; p.row_ctx_len = row_ctx_len; p.num_rows = num_rows;
-    p.out = (bf16*)out; p.error = g_error_dev;
+    p.out = (bf16*)out; p.out32 = out_f32 ? (float*)out : nullptr; p.error = g_error_dev;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.page_size = page_size;
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;

@@ -44,13 +44,13 @@ template <> struct Vec<bf16> {
     }
 };
 
-template <typename T>
+template <typename T, typename TO>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ k_cache,
                        const T* __restrict__ v_cache, const int* __restrict__ block_tables,
                        int table_stride, const int* __restrict__ row_q_start,
                        const int* __restrict__ row_q_len, const int* __restrict__ row_ctx_len,
-                       int num_rows, T* __restrict__ out, int num_heads, int num_kv_heads,
+                       int num_rows, TO* __restrict__ out, int num_heads, int num_kv_heads,
                        int head_dim, int page_size, int page_shift, float scale, int window,
                        int QT, int HG, int min_q_len, int64_t num_pages, int* report) {
     extern __shared__ __align__(16) float smem[];
@@ -160,11 +160,11 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     }
     if (active) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* op = out + ((int64_t)token * num_heads + head) * D;
+        TO* op = out + ((int64_t)token * num_heads + head) * D;
 #pragma unroll
         for (int i = 0; i < ATT_MAX_D / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) op[d] = from_f32<T>(acc[i] * inv);
+            if (d < D) op[d] = from_f32<TO>(acc[i] * inv);
         }
     }
 }
@@ -181,7 +181,7 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows,
                                    int num_tokens, void* out, int act_tag, int num_heads, int num_kv_heads,
                                    int head_dim, int page_size, float scale, int window, int min_q_len,
-                                   long long num_pages, cudaStream_t stream) {
+                                   long long num_pages, int out_f32, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (head_dim < 16 || head_dim > ATT_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -196,16 +196,23 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
     const size_t smem = att_smem_bytes(head_dim);
     cudaError_t e;
     if (act_tag == MIE_F32) {
-        e = cudaFuncSetAttribute(paged_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(paged_attention_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        return launch_kernel(paged_attention_kernel<float>, grid, dim3(ATT_WARPS * 32), smem, stream,
+        return launch_kernel(paged_attention_kernel<float, float>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
             page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
-    } else if (act_tag == MIE_BF16) {
-        e = cudaFuncSetAttribute(paged_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    } else if (act_tag == MIE_BF16 && out_f32) {             // bfloat16 operands, the output left in float32
+        e = cudaFuncSetAttribute(paged_attention_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        return launch_kernel(paged_attention_kernel<bf16>, grid, dim3(ATT_WARPS * 32), smem, stream,
+        return launch_kernel(paged_attention_kernel<bf16, float>, grid, dim3(ATT_WARPS * 32), smem, stream,
+            (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
+            row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
+    } else if (act_tag == MIE_BF16) {
+        e = cudaFuncSetAttribute(paged_attention_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        return launch_kernel(paged_attention_kernel<bf16, bf16>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (bf16*)out, num_heads, num_kv_heads, head_dim,
             page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);

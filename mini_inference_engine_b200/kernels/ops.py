@@ -215,7 +215,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
     for t, n in ((block_tables, "block_tables"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"),
                  (row_ctx_len, "row_ctx_len")):
         _i32(t, n)
-    _need(out.dtype == q.dtype == k_cache.dtype == v_cache.dtype, "q, caches and out must share a type")
+    _need(q.dtype == k_cache.dtype == v_cache.dtype and out.dtype in (q.dtype, torch.float32),
+          "q and caches must share a type; out has it too, or is float32")
     _need(out.is_contiguous(), "attention output must be contiguous")
     rows = row_q_len.numel()
     lib = load("attention_simt")
@@ -223,7 +224,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
                                    _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                    _ptr(row_ctx_len), rows, num_tokens, _ptr(out), tag(q), num_heads,
                                    num_kv_heads, head_dim, page_size, ctypes.c_float(scale),
-                                   int(window or 0), int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), _stream()),
+                                   int(window or 0), int(min_q_len), ctypes.c_longlong(k_cache.shape[0]),
+                                   int(out.dtype == torch.float32 and q.dtype != torch.float32), _stream()),
            "paged_attention")
     return out
 
@@ -236,7 +238,8 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
     Rows with fewer than ``min_q_len`` new tokens are left alone.  ``work`` = (rows, tokens): how many rows have
     ``min_q_len`` tokens or more and their tokens in sum, where the caller knows -- the launch then has blocks for the
     tiles those rows can have, not for every row of the step."""
-    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype and out.dtype in (torch.bfloat16, torch.float32),
+          "prefill attention is bfloat16 (its output bfloat16 or float32)")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the prefill kernel takes multiples of 16 from 16 to 128")
     _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
@@ -249,7 +252,8 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
                                      _ptr(block_tables), block_tables.shape[1], _ptr(row_q_start), _ptr(row_q_len),
                                      _ptr(row_ctx_len), row_q_len.numel(), num_tokens, _ptr(out), num_heads,
                                      num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window or 0),
-                                     int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), *_work_args(work), _stream()),
+                                     int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), *_work_args(work),
+                                     int(out.dtype == torch.float32), _stream()),
            "prefill_attention")
     return out
 
@@ -260,7 +264,8 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
                          min_q_len: int = 2, work=None) -> torch.Tensor:
     """Causal attention of prompt portions on tcgen05 (S and O in tensor memory, operands by TMA);
     head_dim 64 or 128.  ``work``: as for ``prefill_attention``."""
-    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "prefill attention is bfloat16")
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype and out.dtype in (torch.bfloat16, torch.float32),
+          "prefill attention is bfloat16 (its output bfloat16 or float32)")
     _need(head_dim in (64, 128), f"head_dim {head_dim}: the tcgen05 prefill kernel takes 64 and 128")
     _need(q_stride % 8 == 0 and page_size >= 8, "the tcgen05 prefill kernel needs q rows and pages of whole 16-byte pieces")
     _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
@@ -273,7 +278,8 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
                                         ctypes.c_int64(k_cache.shape[0]), _ptr(block_tables), block_tables.shape[1],
                                         _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len), row_q_len.numel(),
                                         num_tokens, _ptr(out), num_heads, num_kv_heads, head_dim, page_size,
-                                        ctypes.c_float(scale), int(window or 0), int(min_q_len), *_work_args(work), _stream()),
+                                        ctypes.c_float(scale), int(window or 0), int(min_q_len), *_work_args(work),
+                                        int(out.dtype == torch.float32), _stream()),
            "prefill_attention_tc")
     return out
 
@@ -435,7 +441,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
     every row (keys ``num_heads`` heads in, values behind them), and the kernel rotates q and the new key by the
     row's position (context length - 1, the whole head as rotary width), uses them, and writes the new key and
     value into the cache -- the separate rotate-and-store launch is not needed then."""
-    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype == out.dtype, "decode attention is bfloat16")
+    _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype and out.dtype in (torch.bfloat16, torch.float32),
+          "decode attention is bfloat16 (its output bfloat16 or float32)")
     _need(head_dim % 16 == 0 and 16 <= head_dim <= 128,
           f"head_dim {head_dim}: the decode kernel takes multiples of 16 from 16 to 128")
     _need(num_heads % num_kv_heads == 0, "query heads must be a multiple of kv heads")
@@ -483,7 +490,8 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     _ptr(part_o), _ptr(part_lse), _ptr(counters), int(stages or 0),
                                     ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]),
                                     int(min_part_tiles if merge == "scratch" else 0),
-                                    _ptr(cos), _ptr(sin), int(cos.shape[0]) if cos is not None else 0, _stream()),
+                                    _ptr(cos), _ptr(sin), int(cos.shape[0]) if cos is not None else 0,
+                                    int(out.dtype == torch.float32), _stream()),
            "decode_attention")
     return out
 
@@ -838,11 +846,12 @@ def diff_combine(maps: torch.Tensor, gate, out: torch.Tensor, *, num_heads: int,
     ``maps`` [T, 2H, DP] for h = g group + i; ``gate`` [T, H] may be a column slice (None: no gate)."""
     T, DP = maps.shape[0], maps.shape[-1]
     _need(maps.is_contiguous() and maps.shape == (T, 2 * num_heads, DP) and DP >= vdim, "maps must be [T, 2H, DP]")
-    _need(out.is_contiguous() and out.shape == (T, num_heads * vdim) and out.dtype == maps.dtype, "out must be contiguous [T, H * vdim]")
+    _need(out.is_contiguous() and out.shape == (T, num_heads * vdim) and maps.dtype in (out.dtype, torch.float32),
+          "out must be contiguous [T, H * vdim]; maps in its type or float32")
     if gate is not None:
-        _need(gate.stride(1) == 1 and gate.shape == (T, num_heads) and gate.dtype == maps.dtype, "gate must be [T, H]")
+        _need(gate.stride(1) == 1 and gate.shape == (T, num_heads) and gate.dtype == out.dtype, "gate must be [T, H]")
     lib = load("diff_attention")
-    _check(lib.mie_diff_combine(_ptr(maps), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+    _check(lib.mie_diff_combine(_ptr(maps), tag(maps), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
                                 tag(out), T, num_heads, group, vdim, DP, ctypes.c_float(lam), ctypes.c_float(eps),
                                 ctypes.c_float(out_scale), _stream()), "diff_combine")
     return out

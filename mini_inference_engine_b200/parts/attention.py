@@ -208,7 +208,9 @@ class DifferentialAttention(Mixer):
     The two maps are run as 2H query heads over 2G key/value heads by the framework's paged attention kernels: the
     rows of 'q' are reordered at load time to [group, map, head in group], so that the kernels' rule "query head / (H / G)"
     finds key head 2g + m, and the rows of 'v' are doubled (each map reads its own copy of the values).  Pages are as wide
-    as the wider of ``dim`` and ``vdim`` (tails zero).  The subtraction, the norm and the gate are one kernel."""
+    as the wider of ``dim`` and ``vdim`` (tails zero).  The kernels leave the maps in float32 (also in bfloat16 mode: where
+    lambda is near 1 the subtraction cancels, and maps rounded to bfloat16 would show); the subtraction, the norm and the
+    gate are one kernel."""
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, diff: float,
                  eps: float, gate: bool = True, shares_kv: bool = False, window: int | None = None):
@@ -267,7 +269,7 @@ class DifferentialAttention(Mixer):
         # (without keys and values of its own the kernel reads the queries only)
         ops.qk_norm_rope(proj, ctx.positions, ctx.slots[cache.group], self.no_freq, q, cache.k, cache.v, num_heads=2 * H,
                          num_kv_heads=2 * G, dim=D, vdim=Dv, rot=0, page_size=cache.page_size, write_cache=writes)
-        maps = self.rt.empty(T, 2 * H, DP)
+        maps = self.rt.empty(T, 2 * H, DP, dtype=torch.float32)       # float32 also in bfloat16 mode: the maps are subtracted
         attn_kernels.attention(q, ctx, cache, maps, 2 * H, 2 * G, DP, self.scale, self.need.mask(), q_stride=2 * H * DP)
         gate_at = 2 * H * D + (0 if self.shares_kv else 2 * G * (D + Dv))
         out = self.rt.empty(T, H * Dv)

@@ -65,8 +65,15 @@ CONFIGS = {
         with_mlp(latent(2, 96, 32, 128, 40, 64, base=1e3), 3, 2, 40),
         with_mlp(delta(2, 1, 128, 48, 5, gate_rank=8), 4, 1, 24),
         with_mlp(attention(2, 2, 128, 64, 0.4), 9, 4, 16)]),
+    # sizes that are multiples of nothing: width 50, latents of 7 and 9, a rotated part of 6 of which 4 rotate, experts of 10,
+    # an odd vocabulary, four copies of the stream, a convolution of two taps, ranks read from tensors of rank 5 and 3
+    "k_d": dict(architecture="Kebudra", vocab=101, width=50, streams=4, embedding=dict(scale=7.0), norm=dict(eps=1e-5), layers=[
+        with_mlp(latent(3, 10, 6, 20, 7, 9, dims=4, base=200.0), 5, 2, 10),
+        with_mlp(attention(3, 1, 12, 20, 0.35), 5, 2, 10),
+        with_mlp(delta(3, 3, 12, 20, 2, decay_rank=5, gate_rank=3), 2, 1, 6),
+        with_mlp(attention(3, 1, 12, 20, 0.7, kv_from=1))]),
 }
-LENGTHS = {"k_a": [5, 77, 130, 2, 49, 24, 25], "k_b": [1, 70, 33, 129, 16, 17, 64], "k_c": [3, 100, 47, 150, 48, 49, 9]}
+LENGTHS = {"k_d": [4, 60, 35, 18, 1, 90, 31], "k_a": [5, 77, 130, 2, 49, 24, 25], "k_b": [1, 70, 33, 129, 16, 17, 64], "k_c": [3, 100, 47, 150, 48, 49, 9]}
 
 
 @pytest.fixture(scope="module")

@@ -137,6 +137,7 @@ ATTENTION_CASES = [
     ("differential_attention", diff_params(num_heads=3, num_kv_heads=3, dim=32, vdim=16, diff=0.5)),       # keys wider than values, no grouping
     ("differential_attention", diff_params(num_heads=2, num_kv_heads=1, dim=64, vdim=64, scale=0.125)),    # heads of 64: the tensor-core kernels
     ("differential_attention", diff_params(num_heads=1, num_kv_heads=1, dim=48, vdim=128, gate=False)),    # one head, heads of 128, no gate
+    ("differential_attention", diff_params(num_heads=2, num_kv_heads=1, dim=24, vdim=160)),                # heads beyond 128: the CUDA-core kernel in both modes
     ("latent_attention", latent_params()),
     ("latent_attention", latent_params(num_heads=1, dim=32, rot_dim=32, vdim=64, rot_dims=16)),            # rotation over half the rotated part
     ("latent_attention", latent_params(num_heads=2, dim=96, rot_dim=32, vdim=48, kv_rank=16, q_rank=8)),   # heads of 128, ranks below the head size
