@@ -2,7 +2,7 @@
 // one wide feed-forward.
 //
 //   router     route with the logits computed in the same kernel: z = W_router x in float32 (float32 weights, the token's
-//              input widened), a block per token, a warp per expert in turn.
+//              input widened), a block per eight tokens, a warp per expert in turn.
 //   route      per token, from float32 router logits z [T, E]: the `top` experts with the largest logits (ties: the lower
 //              index first), weights = softmax over the chosen logits only.  ids [T, top] int32, wts [T, top] float32.
 //   dense_act  with up[t] = [expert 0: F | expert 1: F | ...] the up-projections of ALL experts (one product with the
@@ -53,36 +53,64 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ 
     route_one(z + (int64_t)t * E, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top);
 }
 
-// A block per token: x[t] into shared memory as float32, a warp per expert in turn for the logit, then one thread chooses.
-// `logits` (optional) receives z.
+#define ROUTER_TOKENS 8      // tokens a block: the router's matrix is read once for all of them
+
+// A block per ROUTER_TOKENS tokens: their inputs into shared memory as float32, a warp per expert in turn for the logits of
+// all of them (the expert's row is read once), then a thread per token chooses.  `logits` (optional) receives z.
 template <typename TA>
 __global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                                  float* __restrict__ logits, int h, int E, int top) {
-    extern __shared__ __align__(16) float rs[];               // x [h], then z [E]
-    float* z = rs + h;
+                                  float* __restrict__ logits, int num_tokens, int h, int E, int top, int tpb) {
+    extern __shared__ __align__(16) float rs[];               // x [tpb, h], then z [tpb, E]
+    float* z = rs + (size_t)tpb * h;
     pdl_enter();
-    const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < h; c += blockDim.x) rs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
+    const int t0 = blockIdx.x * tpb, nt = min(tpb, num_tokens - t0);
+    for (int c = threadIdx.x; c < nt * h; c += blockDim.x) rs[c] = to_f32<TA>(x[(int64_t)t0 * h + c]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const bool vec = (h & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
     for (int e = warp; e < E; e += nw) {
         const float* row = w + (int64_t)e * h;
-        float acc = 0.f;
-        if ((h & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
-            for (int c = lane * 4; c < h; c += 128) {
-                const float4 a = *reinterpret_cast<const float4*>(row + c), b = *reinterpret_cast<const float4*>(rs + c);
-                acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
+        float acc[ROUTER_TOKENS];
+#pragma unroll
+        for (int i = 0; i < ROUTER_TOKENS; ++i) acc[i] = 0.f;
+        if (vec) {
+            for (int c0 = lane * 4; c0 < h; c0 += 512) {           // four 16-byte loads of the row in flight
+                float4 a[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    a[u] = c0 + 128 * u < h ? *reinterpret_cast<const float4*>(row + c0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int c = c0 + 128 * u;
+                    if (c >= h) break;
+#pragma unroll
+                    for (int i = 0; i < ROUTER_TOKENS; ++i)
+                        if (i < nt) {
+                            const float4 b = *reinterpret_cast<const float4*>(rs + (size_t)i * h + c);
+                            acc[i] = fmaf(a[u].x, b.x, acc[i]); acc[i] = fmaf(a[u].y, b.y, acc[i]);
+                            acc[i] = fmaf(a[u].z, b.z, acc[i]); acc[i] = fmaf(a[u].w, b.w, acc[i]);
+                        }
+                }
             }
         } else {
-            for (int c = lane; c < h; c += 32) acc = fmaf(row[c], rs[c], acc);
+            for (int c = lane; c < h; c += 32) {
+                const float a = row[c];
+#pragma unroll
+                for (int i = 0; i < ROUTER_TOKENS; ++i)
+                    if (i < nt) acc[i] = fmaf(a, rs[(size_t)i * h + c], acc[i]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc;
+#pragma unroll
+        for (int i = 0; i < ROUTER_TOKENS; ++i) {
+            const float v = warp_sum(acc[i]);
+            if (lane == 0 && i < nt) z[i * E + e] = v;
+        }
     }
     __syncthreads();
     if (logits)
-        for (int e = threadIdx.x; e < E; e += blockDim.x) logits[(int64_t)t * E + e] = z[e];
-    if (threadIdx.x == 0) route_one(z, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top);
+        for (int c = threadIdx.x; c < nt * E; c += blockDim.x) logits[(int64_t)t0 * E + c] = z[c];
+    if (threadIdx.x < nt)
+        route_one(z + threadIdx.x * E, ids + (int64_t)(t0 + threadIdx.x) * top, wts + (int64_t)(t0 + threadIdx.x) * top, E, top);
 }
 
 __device__ __forceinline__ float expert_act(float x, int kind) {
@@ -344,16 +372,19 @@ extern "C" int mie_moe_router(const void* x, int tag, const float* w, int* ids, 
                               int top, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || h <= 0) return MIE_ERR_BAD_ARG;
-    const size_t smem = (size_t)(h + E) * sizeof(float);
+    int tpb = ROUTER_TOKENS;                                   // fewer where the tokens' inputs would not fit in 96 KB ...
+    while (tpb > 1 && (size_t)tpb * (h + E) * sizeof(float) > 96 * 1024) tpb >>= 1;
+    while (tpb > 1 && (num_tokens + tpb - 1) / tpb < device_sm_count()) tpb >>= 1;      // ... or would leave SMs without a block
+    const size_t smem = (size_t)tpb * (h + E) * sizeof(float);
     if (smem > 200 * 1024) return MIE_ERR_TOO_LARGE;
-    const int threads = 256;
+    const int threads = 256, blocks = (num_tokens + tpb - 1) / tpb;
     cudaError_t e;
     if (tag == MIE_F32) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<float>, dim3(num_tokens), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, h, E, top);
+        return launch_kernel(moe_router_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb);
     } else if (tag == MIE_BF16) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<bf16>, dim3(num_tokens), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, h, E, top);
+        return launch_kernel(moe_router_kernel<bf16>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb);
     }
     return MIE_ERR_BAD_ARG;
 }
