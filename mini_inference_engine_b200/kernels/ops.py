@@ -1048,6 +1048,4 @@ def grouped_linear(rows: torch.Tensor, b: torch.Tensor, ends: torch.Tensor) -> t
     grouped product (float32 accumulation), as the plain products of prompt-sized steps are the library's."""
     _need(rows.is_cuda and rows.dtype == torch.bfloat16 == b.dtype and rows.is_contiguous() and ends.dtype == torch.int32,
           "grouped product: bfloat16 rows and matrices on the device, int32 ends")
-    global launches
-    launches += 1
-    return torch._grouped_mm(rows, b, offs=ends)
+    return torch._grouped_mm(rows, b, offs=ends)          # (not counted in ``launches``: that counts this package's own kernels)
