@@ -127,14 +127,15 @@ __device__ __forceinline__ void cp_async16(float* dst_smem, const float* src) {
 // padded to whole 16-byte pieces.  A lane holds R entries of its column: few, so that a column's sums are spread
 // over many lanes and an SM holds many warps whose chains hide one another's latency.  VEC: D = L * R and D % 4 = 0, so the
 // ring is filled and read 16 bytes at a time and nothing needs a bound check; otherwise everything goes entry by entry.
-template <int R, bool VEC>
+template <int R, bool VEC, int LT>
 __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vn,
                                   const float* __restrict__ beta, const float* __restrict__ decay, const float* __restrict__ kq,
                                   const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
                                   const int* __restrict__ state_slots, float* __restrict__ state, float* __restrict__ out, int H,
-                                  int G, int D, int Dv, int L, int cols, int tb, int slot_floats) {
+                                  int G, int D, int Dv, int L_rt, int cols, int tb, int slot_floats) {
     extern __shared__ __align__(16) float ring[];
     pdl_enter();
+    const int L = LT > 0 ? LT : L_rt;                         // lanes a column: a constant where the launcher knows it (shifts, unrolled sums)
     const int row = blockIdx.x, h = blockIdx.y;
     const int l = threadIdx.x % L, cl = threadIdx.x / L, j0 = blockIdx.z * cols, j = j0 + cl;
     const bool active = cl < cols && j < Dv;                   // threads that only fill up the last warp own no column
@@ -224,9 +225,17 @@ __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __r
             }
             r1 += r1b;
             r2 += r2b;
-            for (int o = L >> 1; o > 0; o >>= 1) {
-                r1 += __shfl_xor_sync(0xffffffffu, r1, o);
-                r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+            if constexpr (LT > 0) {
+#pragma unroll
+                for (int o = LT >> 1; o > 0; o >>= 1) {
+                    r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                    r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+                }
+            } else {
+                for (int o = L >> 1; o > 0; o >>= 1) {
+                    r1 += __shfl_xor_sync(0xffffffffu, r1, o);
+                    r2 += __shfl_xor_sync(0xffffffffu, r2, o);
+                }
             }
             const float u = op[3 * D + cols] * (v_on * op[v_at] - r1);
 #pragma unroll
@@ -323,7 +332,8 @@ static int launch_scan(const float* qn, const float* kn, const float* vn, const 
     const size_t smem = (size_t)DELTA_BATCHES * tb * slot_bytes;
     const bool vec = D == L * R && D % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(decay)) & 15) == 0;
-    auto kernel = vec ? delta_scan_kernel<R, true> : delta_scan_kernel<R, false>;
+    // the vectorised kernel with the lanes a column as a constant for the common key sizes (64 and 128: 16 lanes), else at run time
+    auto kernel = !vec ? delta_scan_kernel<R, false, 0> : (L == 16 ? delta_scan_kernel<R, true, 16> : delta_scan_kernel<R, true, 0>);
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
