@@ -192,6 +192,7 @@ __global__ void delta_scan_kernel(const float* __restrict__ qn, const float* __r
         __syncthreads();                                       // ... and everybody else's
         const float* base = ring + (size_t)(batch % DELTA_BATCHES) * tb * slot_floats;
         const int first = batch * tb, count = min(tb, n - first);
+#pragma unroll 4                                              // the next tokens' operands are read while a token's sums travel
         for (int tok = 0; tok < count; ++tok) {
             const float* op = base + tok * slot_floats;
             float k[R], q[R], g[R];
