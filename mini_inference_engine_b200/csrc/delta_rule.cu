@@ -62,6 +62,21 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, int64_t stride,
                           : (unit < G ? qn + (int64_t)t * G * D + unit * D : kn + (int64_t)t * G * D + (unit - G) * D);
         if (is_v) {
             for (int d = lane; d < n; d += 32) dst[d] = conv_at<T>(proj, stride, taps, st, C, K, t, local, c0 + d);
+        } else if (n <= 256) {                                        // a head of up to 256 entries stays in registers between its two passes
+            float y[8];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int d = lane + 32 * i;
+                y[i] = d < n ? conv_at<T>(proj, stride, taps, st, C, K, t, local, c0 + d) : 0.f;
+                ss = fmaf(y[i], y[i], ss);
+            }
+            const float s = (unit < G ? q_scale : 1.0f) / sqrtf(warp_sum(ss) + unit_eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int d = lane + 32 * i;
+                if (d < n) dst[d] = y[i] * s;
+            }
         } else {
             float ss = 0.f;
             for (int d = lane; d < n; d += 32) {
