@@ -306,3 +306,35 @@ def test_router_takes_the_largest_logits_and_weighs_by_their_softmax():
         assert torch.allclose(logits, want, atol=1e-4, rtol=1e-5)
         ids3, w3 = ops.moe_route(want.contiguous(), 4)
         assert torch.equal(ids2, ids3) and torch.allclose(w2, w3, atol=1e-5)
+
+
+@pytest.mark.parametrize("dim,vdim", [(16, 32), (64, 64), (48, 128), (24, 160)])
+def test_attention_kernels_leave_their_output_in_float32(dim, vdim, monkeypatch):
+    """The option that differential attention uses in bfloat16 mode: every paged attention kernel (decoding, portions on
+    mma.sync and on tcgen05, the CUDA-core kernel for wide heads) writes float32 when handed a float32 output; rounded to
+    bfloat16 it is what the kernel writes otherwise."""
+    from mini_inference_engine_b200.parts import attention as part
+    rt = rt_for(torch.bfloat16)
+    params = diff_params(num_heads=2, num_kv_heads=1, dim=dim, vdim=vdim)
+    mixer = build("mixer", "differential_attention", **params)
+    bind_random(mixer, rt, 16)
+    h = Harness(mixer, rt, pages=12, slots=1)
+    seen = []
+    plain = part.attn_kernels.attention
+
+    def both(q, ctx, cache, out, *a, **k):
+        plain(q, ctx, cache, out, *a, **k)
+        rounded = torch.empty_like(out, dtype=torch.bfloat16)
+        plain(q, ctx, cache, rounded, *a, **k)
+        seen.append((out.clone(), rounded))
+        return out
+
+    monkeypatch.setattr(part.attn_kernels, "attention", both)
+    x = inputs(70, params["hidden_size"], 5, torch.bfloat16)
+    run_in_portions(h, x, [40, 1, 1, 27, 1])             # portions and single tokens: both kinds of kernel
+    assert len(seen) == 5
+    for f32, b16 in seen:
+        assert f32.dtype == torch.float32 and torch.isfinite(f32).all()
+        err = (f32 - b16.float()).abs().max().item()
+        assert err <= 2 ** -7 * max(f32.abs().max().item(), 1e-6), f"float32 and bfloat16 outputs differ by {err:.3e}"
+        assert (f32 != f32.bfloat16().float()).any(), "the float32 output carries more than bfloat16 holds"
